@@ -5,6 +5,7 @@ from .spec import BlockSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedul
 from .qwen3 import Qwen3Config
 from .gigopel import GigopelConfig
 from .sokirax import SokiraxConfig
+from .felolorn import FelolornConfig
 
 __all__ = ["ConfigError", "config_from_dict", "load_config", "register_architecture", "registered_architectures",
-           "BlockSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule", "Qwen3Config", "GigopelConfig", "SokiraxConfig"]
+           "BlockSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule", "Qwen3Config", "GigopelConfig", "SokiraxConfig", "FelolornConfig"]

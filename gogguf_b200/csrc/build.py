@@ -57,6 +57,7 @@ MODULES: Dict[str, str] = {
     "latent_attention": "latent_attention.cu",
     "moe": "moe.cu",
     "retention": "retention.cu",
+    "recurrence": "recurrence.cu",
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_fast": "attention_fast.cu",

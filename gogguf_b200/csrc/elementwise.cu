@@ -11,7 +11,7 @@
 // ----------------------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* tokens,
-                                    float* __restrict__ out, int H, int V) {
+                                    float* __restrict__ out, int H, int V, float scale) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
@@ -22,15 +22,15 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* tok
         return;
     }
     const TW* r = table + (size_t)tok * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f<TW>(r[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f<TW>(r[i]) * scale;
 }
 
 GG_API gg_embed_gather(const void* table, int table_dtype, const int* tokens, float* out,
-                       int T, int H, int V, cudaStream_t stream) {
+                       int T, int H, int V, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || V <= 0) return GG_ERR_ARG;
     GG_DISPATCH_DTYPE(table_dtype, TW,
-        gg_launch(embed_gather_kernel<TW>, dim3(T), dim3(256), 0, stream, 1, (const TW*)table, tokens, out, H, V));
+        gg_launch(embed_gather_kernel<TW>, dim3(T), dim3(256), 0, stream, 1, (const TW*)table, tokens, out, H, V, scale));
     return gg_last_error();
 }
 
@@ -498,7 +498,8 @@ GG_API gg_qkv_prep(const void* qkv, int dtype, void* q_out, const float* qw, con
 // part needs no kernel of its own.
 __global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, float* y, const float* __restrict__ w,
                                                           int H, float eps, bf16* __restrict__ xhat,
-                                                          float* __restrict__ ssq, int parts, int zero_y) {
+                                                          float* __restrict__ ssq, int parts, int zero_y,
+                                                          const float* gate, const float* __restrict__ gate_bias) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[33];
@@ -506,7 +507,14 @@ __global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, float* y, co
     const size_t r = blockIdx.x;
     float* yr = y + r * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = yr[i]; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = yr[i];
+        if (gate != nullptr) {               // the gated row replaces the raw one: the second pass reads it back
+            v *= 1.0f / (1.0f + expf(-(gate[r * H + i] + (gate_bias != nullptr ? gate_bias[i] : 0.f))));
+            yr[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
     ss = block_sum(ss, red);
     const float f = 1.0f / sqrtf(ss / (float)H + eps);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -534,9 +542,12 @@ __global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, float* y, co
 
 // The same with 16-byte accesses (H a multiple of 4, rows on 16-byte boundaries): a thread owns four columns, a
 // warp the 128 columns of one block of the sums of squares, so those need no shared memory.
+__device__ __forceinline__ float gate_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
 __global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, float* y, const float* __restrict__ w,
                                                                int H, float eps, bf16* __restrict__ xhat,
-                                                               float* __restrict__ ssq, int parts, int zero_y) {
+                                                               float* __restrict__ ssq, int parts, int zero_y,
+                                                               const float* gate, const float* __restrict__ gate_bias) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[33];
@@ -547,7 +558,16 @@ __global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, float* 
     const int n4 = H >> 2;
     float ss = 0.f;
     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-        const float4 v = yr[i];
+        float4 v = yr[i];
+        if (gate != nullptr) {               // the gated row replaces the raw one: the second pass reads it back
+            float4 g = reinterpret_cast<const float4*>(gate + r * H)[i];
+            if (gate_bias != nullptr) {
+                const float4 gb = reinterpret_cast<const float4*>(gate_bias)[i];
+                g.x += gb.x; g.y += gb.y; g.z += gb.z; g.w += gb.w;
+            }
+            v.x *= gate_sigmoid(g.x); v.y *= gate_sigmoid(g.y); v.z *= gate_sigmoid(g.z); v.w *= gate_sigmoid(g.w);
+            yr[i] = v;
+        }
         ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
     }
     ss = block_sum(ss, red);
@@ -578,23 +598,28 @@ __global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, float* 
 }
 
 // xhat (bfloat16 [rows, H]) and ssq (float32 [rows, ceil(H / 128)]) may both be null.  zero_y != 0: y is left
-// zeroed (the buffer the next part of the block adds its output into, without a fill of its own).
+// zeroed (the buffer the next part of the block adds its output into, without a fill of its own).  gate (float32
+// [rows, H], may be null) with gate_bias ([H], may be null): y is first multiplied by sigmoid(gate + gate_bias),
+// element by element, and the norm is taken of the product.
 GG_API gg_rmsnorm_add(float* x, float* y, const float* w, int rows, int H, float eps, void* xhat, float* ssq,
-                      int zero_y, cudaStream_t stream) {
+                      int zero_y, const float* gate, const float* gate_bias, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H <= 0 || (xhat == nullptr) != (ssq == nullptr)) return GG_ERR_ARG;
     const int parts = (H + 127) / 128;
-    if ((H & 3) == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)w) & 15) == 0 && (((uintptr_t)xhat) & 7) == 0) {
+    if ((H & 3) == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)w | (uintptr_t)gate | (uintptr_t)gate_bias) & 15) == 0 &&
+        (((uintptr_t)xhat) & 7) == 0) {
         // few rows (decode steps): as many threads as the row has groups of four columns, up to 1,024
         int threads = ((H >> 2) + 31) / 32 * 32;
         if (threads > 1024 || rows >= 512) threads = threads > 256 ? 256 : threads;
-        gg_launch(rmsnorm_add_vec_kernel, dim3(rows), dim3(threads), 0, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts, zero_y);
+        gg_launch(rmsnorm_add_vec_kernel, dim3(rows), dim3(threads), 0, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts, zero_y,
+                  gate, gate_bias);
         return gg_last_error();
     }
     // (a block of 128 columns whose tail lies beyond H gets zeros from the warps that have no column)
     const size_t smem = ssq != nullptr ? ((size_t)(parts + 1) * 4) * sizeof(float) : 0;
     if (smem > 48 * 1024) return GG_ERR_ARG;
-    gg_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), smem, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts, zero_y);
+    gg_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), smem, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts, zero_y,
+              gate, gate_bias);
     return gg_last_error();
 }
 
@@ -750,6 +775,128 @@ __global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restri
 GG_API gg_feed_tokens(int* tokens, const int* src, const int* sampled, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
     return gg_launch(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, tokens, src, sampled, n);
+}
+
+// ----------------------------------------------------------------------------- short causal convolution over time
+// out[t, c] = h[t, c] * keep + sum_j w[c, j] * h[t - taps + 1 + j, c] (j < taps; the last tap meets the token
+// itself), per channel, inside each sequence; keep = 1 adds the convolution to its input.  Rows before the step's
+// first token come from the sequence's state [slot][taps - 1][W] (float32: the last taps - 1 input rows of the
+// sequence in order, zeros at its start).  One block per token.  The state is not written here: other blocks of
+// the same sequence still read it (short_conv_state_kernel moves it on afterwards).
+template <typename T>
+__global__ void __launch_bounds__(256) short_conv_kernel(const T* h, T* out, const float* __restrict__ w,
+                                                         const float* state, const int* __restrict__ cu_seqlens,
+                                                         const int* __restrict__ slots, const int* __restrict__ seq_of_token,
+                                                         int W, int taps, float keep) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = seq_of_token[t];
+    T* o = out + (size_t)t * W;
+    if (b < 0) {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) o[c] = from_f<T>(0.f);
+        return;
+    }
+    const int start = cu_seqlens[b];
+    const int R = taps - 1;
+    const float* st = state + (size_t)slots[b] * R * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float* wc = w + (size_t)c * taps;
+        float acc = to_f<T>(h[(size_t)t * W + c]) * (keep + wc[R]);
+        for (int j = 0; j < R; ++j) {
+            const int s = t - R + j;
+            const float v = s >= start ? to_f<T>(h[(size_t)s * W + c]) : st[(size_t)(R + (s - start)) * W + c];
+            acc = fmaf(wc[j], v, acc);
+        }
+        o[c] = from_f<T>(acc);
+    }
+}
+
+// The state after the step: the last taps - 1 input rows of every sequence (rows of the step where it brought
+// that many, else the old state moved up).  One block per sequence; a thread reads all it needs of a channel
+// before it writes.  Padding sequences (seq_of_token < 0 at their first row) are left alone.
+#define CONV_MAX_TAPS 16
+template <typename T>
+__global__ void __launch_bounds__(256) short_conv_state_kernel(const T* h, float* state, const int* __restrict__ cu_seqlens,
+                                                               const int* __restrict__ slots,
+                                                               const int* __restrict__ seq_of_token, int W, int taps) {
+    pdl_launch();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+    if (n <= 0 || seq_of_token[start] < 0) return;
+    const int R = taps - 1;
+    float* st = state + (size_t)slots[b] * R * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float keep[CONV_MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j < R) {
+                const int rel = n - R + j;
+                keep[j] = rel >= 0 ? to_f<T>(h[(size_t)(start + rel) * W + c]) : st[(size_t)(R + rel) * W + c];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)
+            if (j < R) st[(size_t)j * W + c] = keep[j];
+    }
+}
+
+// h and out [T, W] in `dtype` (they may not overlap), w [W][taps] float32, state [slots][taps - 1][W] float32.
+GG_API gg_short_conv(const void* h, void* out, int dtype, const float* w, float* state, const int* cu_seqlens,
+                     const int* slots, const int* seq_of_token, int ntok, int n_seqs, int W, int taps, float keep,
+                     cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (W <= 0 || taps < 1 || taps > CONV_MAX_TAPS || (taps > 1 && state == nullptr)) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(short_conv_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, (const T*)h, (T*)out, w, (const float*)state,
+                  cu_seqlens, slots, seq_of_token, W, taps, keep);
+        if (taps > 1)
+            gg_launch(short_conv_state_kernel<T>, dim3(n_seqs), dim3(256), 0, stream, 1, (const T*)h, state, cu_seqlens,
+                      slots, seq_of_token, W, taps));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- RMS norm of strided rows
+// out[t, :n] = x[t, :n] / sqrt(mean(x[t, :n]^2) + eps) * w, rows of x ldx apart and of out ldo apart; the sums in
+// float32.  One block per row (the latent of a projection's output, normed before the next projection).
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const T* x, long long ldx, const float* __restrict__ w, T* out,
+                                                           long long ldo, int n, float eps) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const T* xr = x + (size_t)blockIdx.x * ldx;
+    T* o = out + (size_t)blockIdx.x * ldo;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f<T>(xr[i]); ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float f = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f<T>(to_f<T>(xr[i]) * f * w[i]);
+}
+
+GG_API gg_rmsnorm_rows(const void* x, long long ldx, int dtype, const float* w, void* out, long long ldo, int rows, int n,
+                       float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0 || ldx < n || ldo < n) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(rmsnorm_rows_kernel<T>, dim3(rows), dim3(256), 0, stream, 1, (const T*)x, ldx, w, (T*)out, ldo, n, eps));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- soft cap
+// z <- cap * tanh(z / cap), in place, float32 (logits that are bounded smoothly).
+__global__ void softcap_kernel(float* z, float cap, long long n) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) z[i] = cap * tanhf(z[i] / cap);
+}
+
+GG_API gg_softcap(float* z, float cap, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return GG_ERR_ARG;
+    return gg_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, z, cap, n);
 }
 
 // 1 if this library was built with checked page tables (the debug build), else 0.

@@ -26,7 +26,8 @@ def latent_attention_mma(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tens
                          positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor,
                          page_size: int, n_seqs: int, n_tokens: int, heads: int, R: int, r: int, scale: float,
                          window: int, splits: int = 1, part_o: Optional[torch.Tensor] = None,
-                         part_ml: Optional[torch.Tensor] = None, max_new: Optional[int] = None) -> None:
+                         part_ml: Optional[torch.Tensor] = None, max_new: Optional[int] = None,
+                         sink: Optional[torch.Tensor] = None) -> None:
     """splits > 1 cuts every CTA's range of cached positions into that many shares (steps with few CTAs); part_o
     float32 [n_tokens * heads, splits, R] and part_ml [n_tokens * heads, splits, 2] take the partial results.
     max_new: the most new tokens any sequence brings (default: all could be one sequence's); a step of few rows
@@ -40,7 +41,8 @@ def latent_attention_mma(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tens
         seq_of_token.data_ptr(), page_table.data_ptr(), page_table.shape[-1], int(page_size), pool.shape[0],
         int(n_seqs), int(n_tokens), heads, R, r, float(scale), int(window), int(splits),
         part_o.data_ptr() if part_o is not None else 0, part_ml.data_ptr() if part_ml is not None else 0,
-        int(max_new) if max_new is not None else int(n_tokens), status_word(qcat.device).data_ptr(),
+        int(max_new) if max_new is not None else int(n_tokens), sink.data_ptr() if sink is not None else 0,
+        status_word(qcat.device).data_ptr(),
         torch.cuda.current_stream().cuda_stream)
 
 
@@ -51,7 +53,8 @@ def mma_splits(n_seqs: int, n_tokens: int, heads: int, R: int, r: int, window: i
 
 def latent_prompt_mma(qd: torch.Tensor, qcat: torch.Tensor, kv: torch.Tensor, ckr: torch.Tensor, av: torch.Tensor,
                       cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor, n_seqs: int, n_tokens: int, heads: int,
-                      d: int, r: int, dv: int, R: int, scale: float, window: int, out_scale: float = 1.0) -> None:
+                      d: int, r: int, dv: int, R: int, scale: float, window: int, out_scale: float = 1.0,
+                      sink: Optional[torch.Tensor] = None) -> None:
     """Attention of a step whose sequences all start at position 0, in the expanded form: qd [T, >= heads (d + r)]
     (plain query parts), qcat [T, heads, R + r] (rotated parts at [..., R:]), kv [T, heads d + heads dv] (per-head
     plain keys, then values), ckr [T, R + r] (the shared rotated key part at [:, R:]); av [T, heads, dv] receives
@@ -62,7 +65,8 @@ def latent_prompt_mma(qd: torch.Tensor, qcat: torch.Tensor, kv: torch.Tensor, ck
     kernel("latent_attention", "gg_latent_prompt_mma")(
         qd.data_ptr(), qd.stride(0), qcat.data_ptr(), kv.data_ptr(), kv.stride(0), ckr.data_ptr(), ckr.stride(0),
         av.data_ptr(), cu_seqlens.data_ptr(), seq_of_token.data_ptr(), int(n_seqs), int(n_tokens), heads, d, r, dv, R,
-        float(scale), int(window), float(out_scale), torch.cuda.current_stream().cuda_stream)
+        float(scale), int(window), float(out_scale), sink.data_ptr() if sink is not None else 0,
+        torch.cuda.current_stream().cuda_stream)
 
 
 def prompt_takes(d: int, r: int, dv: int) -> bool:
@@ -74,8 +78,9 @@ def mma_takes(R: int, r: int) -> bool:
 
 
 class _Fast:
-    def __init__(self, heads: int, R: int, r: int, scale: float, window: int):
+    def __init__(self, heads: int, R: int, r: int, scale: float, window: int, sink: Optional[torch.Tensor] = None):
         self.H, self.R, self.r, self.scale, self.window = heads, R, r, scale, window
+        self.sink = sink            # float32 [heads] or None: a term of the softmax's denominator per head
 
     def absorb(self, qd: torch.Tensor, ldx: int, hx: int, uk_t: torch.Tensor, qcat: torch.Tensor, m: int) -> None:
         """qcat[t, h, :R] = Wuk_h^T q_plain[t, h]."""
@@ -92,7 +97,7 @@ class _Fast:
             part_ml = ctx.ws.get("lat_part_ml", (T * H, splits, 2), torch.float32)
         latent_attention_mma(qcat, pool, out, ctx.cu_seqlens, ctx.positions, ctx.seq_of_token, table, page_size,
                              ctx.n_seqs, T, H, R, self.r, self.scale, self.window, splits, part_o, part_ml,
-                             max_new=max(int(ctx.max_new), 1))
+                             max_new=max(int(ctx.max_new), 1), sink=self.sink)
 
     def expand(self, olat: torch.Tensor, uv: torch.Tensor, av: torch.Tensor, m: int, alpha: float) -> None:
         """av[t, h, :] = alpha * Wuv_h olat[t, h]."""
@@ -101,9 +106,9 @@ class _Fast:
 
 
 def try_make(heads: int, nope_dim: int, latent_dim: int, rope_dim: int, row_stride: int, scale: float,
-             window: int) -> Optional[_Fast]:
+             window: int, sink: Optional[torch.Tensor] = None) -> Optional[_Fast]:
     """The tensor-core forms for bfloat16, or None when the sizes are outside what they take (latent and rotated
     sizes multiples of 16, every row of the q / down product on a 16-byte boundary); the plain kernels then serve."""
     if nope_dim % 8 or (nope_dim + rope_dim) % 8 or row_stride % 8 or not mma_takes(latent_dim, rope_dim):
         return None
-    return _Fast(heads, latent_dim, rope_dim, scale, window)
+    return _Fast(heads, latent_dim, rope_dim, scale, window, sink)

@@ -43,13 +43,13 @@ def _need(t: torch.Tensor, dt: torch.dtype, what: str) -> None:
 
 
 # ------------------------------------------------------------------------------- elementwise
-def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] (float32) = table[tokens[t], :]; negative ids give zero rows."""
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] (float32) = table[tokens[t], :] * scale; negative ids give zero rows."""
     _need(tokens, torch.int32, "tokens")
     _need(out, torch.float32, "out")
     V, H = table.shape
     kernel("elementwise", "gg_embed_gather")(_p(table), dtype_code(table.dtype), _p(tokens), _p(out),
-                                              tokens.numel(), H, V, _stream())
+                                              tokens.numel(), H, V, float(scale), _stream())
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -132,8 +132,10 @@ def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Te
 
 
 def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
-                xhat: Optional[torch.Tensor] = None, ssq: Optional[torch.Tensor] = None, zero_y: bool = False) -> None:
-    """x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight, all float32.  With `xhat` (bfloat16 like x) and `ssq`
+                xhat: Optional[torch.Tensor] = None, ssq: Optional[torch.Tensor] = None, zero_y: bool = False,
+                gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> None:
+    """x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight, all float32.  With `gate` (float32 like y) and `gate_bias`
+    (float32 [H], optional) y is first multiplied by sigmoid(gate + gate_bias), and the norm is the product's.  With `xhat` (bfloat16 like x) and `ssq`
     (float32 [rows, ceil(H / 128)]) the updated rows' bfloat16 copy and sums of squares per 128 columns are left too
     (what `row_stats` makes).  zero_y: y is left zeroed."""
     _need(x, torch.float32, "x")
@@ -149,8 +151,54 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
         _need(ssq, torch.float32, "ssq")
         if xhat.numel() != x.numel() or ssq.numel() != (x.numel() // H) * ((H + 127) // 128):
             raise KernelError("rmsnorm_add: shapes of xhat / ssq disagree")
+    if gate is not None:
+        _need(gate, torch.float32, "gate")
+        if gate.shape != y.shape:
+            raise KernelError("rmsnorm_add: the gate has the shape of y")
+        if gate_bias is not None:
+            _need(gate_bias, torch.float32, "gate bias")
+            if gate_bias.numel() != H:
+                raise KernelError("rmsnorm_add: the gate's bias has one number per column")
+    elif gate_bias is not None:
+        raise KernelError("rmsnorm_add: a gate bias without a gate")
     kernel("elementwise", "gg_rmsnorm_add")(_p(x), _p(y), _p(weight), x.numel() // H, H, float(eps), _p(xhat), _p(ssq),
-                                             int(zero_y), _stream())
+                                             int(zero_y), _p(gate), _p(gate_bias), _stream())
+
+
+def short_conv(h: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor],
+               cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor, n_tokens: int, n_seqs: int,
+               keep: float = 1.0) -> None:
+    """out[t] = keep * h[t] + sum_j weight[:, j] * h[t - taps + 1 + j] per channel inside each sequence; rows before
+    the step come from state [slots, taps - 1, W] (float32), which is then moved on to the step's last rows."""
+    W, taps = weight.shape
+    if h.dtype != out.dtype or not h.is_contiguous() or not out.is_contiguous() or h.shape[-1] != W:
+        raise KernelError("short_conv: h and out are contiguous [T, W] of one dtype")
+    if h.data_ptr() == out.data_ptr():
+        raise KernelError("short_conv: out may not be h")
+    _need(weight, torch.float32, "taps")
+    if taps > 1:
+        _need(state, torch.float32, "state")
+        if tuple(state.shape[1:]) != (taps - 1, W):
+            raise KernelError("short_conv: the state is [slots, taps - 1, W]")
+    kernel("elementwise", "gg_short_conv")(_p(h), _p(out), dtype_code(h.dtype), _p(weight), _p(state), _p(cu_seqlens),
+                                            _p(slots), _p(seq_of_token), int(n_tokens), int(n_seqs), W, taps, float(keep),
+                                            _stream())
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows: int) -> None:
+    """out[t] = x[t] / rms(x[t]) * weight for rows that may be column ranges of wider buffers (same dtype)."""
+    n = weight.numel()
+    if x.dtype != out.dtype or x.stride(-1) != 1 or out.stride(-1) != 1 or x.shape[-1] != n or out.shape[-1] != n:
+        raise KernelError("rmsnorm_rows: x and out are [T, n] views of one dtype with unit column stride")
+    _need(weight, torch.float32, "norm weight")
+    kernel("elementwise", "gg_rmsnorm_rows")(_p(x), x.stride(0), dtype_code(x.dtype), _p(weight), _p(out), out.stride(0),
+                                              int(rows), n, float(eps), _stream())
+
+
+def softcap(z: torch.Tensor, cap: float, n: Optional[int] = None) -> None:
+    """z <- cap * tanh(z / cap) in place (float32)."""
+    _need(z, torch.float32, "logits")
+    kernel("elementwise", "gg_softcap")(_p(z), float(cap), int(z.numel() if n is None else n), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_tokens: int, inter: int) -> None:
@@ -264,12 +312,16 @@ def headwise_gemm(x: torch.Tensor, ldx: int, hx: int, w: torch.Tensor, out: torc
 
 def latent_attention_plain(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                            seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int, n_tokens: int,
-                           heads: int, R: int, r: int, scale: float, window: int) -> None:
+                           heads: int, R: int, r: int, scale: float, window: int,
+                           sink: Optional[torch.Tensor] = None) -> None:
+    """sink (float32 [heads], optional): exp(sink_h) joins the softmax's denominator, without key or value."""
     from .tcgen05_gemm import status_word
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
     kernel("latent_attention", "gg_latent_attention_plain")(
         _p(qcat), dtype_code(qcat.dtype), _p(pool), dtype_code(pool.dtype), pool.shape[-1], _p(out),
         dtype_code(out.dtype), _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], int(page_size),
-        pool.shape[0], n_tokens, heads, R, r, float(scale), int(window), _p(status_word(qcat.device)), _stream())
+        pool.shape[0], n_tokens, heads, R, r, float(scale), int(window), _p(sink), _p(status_word(qcat.device)), _stream())
 
 
 # ------------------------------------------------------------------------------- retention
@@ -334,6 +386,55 @@ def retention_chunks(qkvg: torch.Tensor, out: torch.Tensor, scratch: torch.Tenso
         int(rot), float(key_scale), float(eps), float(out_scale), _stream())
 
 
+# ------------------------------------------------------------------------------- linear recurrences
+def gated_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, raw: torch.Tensor, state: torch.Tensor,
+               cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor, n_tokens: int, n_seqs: int,
+               heads: int, d: int, dv: int, decay: Optional[torch.Tensor] = None,
+               forget_bias: Optional[torch.Tensor] = None, forget_lower: Optional[torch.Tensor] = None,
+               act_q: int = 0, act_k: int = 0, act_v: int = 0) -> None:
+    """S_t = diag(g_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head over the step's tokens, sequence by sequence,
+    from and into state [slots, heads, d, dv] (float32); raw [T, heads * dv] (float32) gets o_t.  x [T, ld] holds
+    the projections: q heads at column q_off, v heads at v_off; with `decay` ([heads]) g is that number and the k
+    heads are at k_off; with `forget_bias` and `forget_lower` ([heads * d]) the columns at k_off are the forget
+    gate's pre-activation z, f = lower + (1 - lower) sigmoid(z + bias), g = f and k = 1 - f.  act_*: 0 as it is,
+    1 silu (csrc/recurrence.cu)."""
+    if x.stride(-1) != 1:
+        raise KernelError("gated_scan: rows of x must be contiguous")
+    _need(raw, torch.float32, "raw")
+    _need(state, torch.float32, "state")
+    if tuple(state.shape[1:]) != (heads, d, dv) or raw.shape[-1] != heads * dv:
+        raise KernelError("gated_scan: the state must be [slots, heads, d, dv] and raw [T, heads * dv]")
+    gate = 0 if decay is not None else 1
+    for t, n in ((decay, heads), (forget_bias, heads * d), (forget_lower, heads * d)):
+        if t is not None:
+            _need(t, torch.float32, "recurrence constants")
+            if t.numel() != n:
+                raise KernelError("gated_scan: decay is [heads], the forget gate's bias and lower bound [heads * d]")
+    kernel("recurrence", "gg_gated_scan")(
+        _p(x), dtype_code(x.dtype), x.stride(0), int(q_off), int(k_off), int(v_off), _p(raw), _p(state), _p(cu_seqlens),
+        _p(slots), _p(seq_of_token), _p(decay), _p(forget_bias), _p(forget_lower), gate, int(n_tokens), int(n_seqs),
+        int(heads), int(d), int(dv), int(act_q), int(act_k), int(act_v), _stream())
+
+
+def scan_finish(raw: torch.Tensor, x: Optional[torch.Tensor], g_off: int, out: torch.Tensor,
+                weight: Optional[torch.Tensor], seq_of_token: torch.Tensor, n_tokens: int, heads: int, dv: int,
+                eps: float, out_scale: float = 1.0, whole: bool = False, gate: int = 0) -> None:
+    """out[t] = norm(raw[t]) * gate * out_scale in the dtype of `out`: every head over its dv outputs with weight
+    [dv], or (whole) all heads together with weight [heads * dv]; gate 0 none, 1 sigmoid, 2 silu of x[t, g_off:]."""
+    _need(raw, torch.float32, "raw")
+    if not out.is_contiguous() or out.shape[-1] != heads * dv:
+        raise KernelError("scan_finish: out is contiguous [T, heads * dv]")
+    if weight is not None:
+        _need(weight, torch.float32, "norm weight")
+        if weight.numel() != (heads * dv if whole else dv):
+            raise KernelError("scan_finish: the weight's size does not fit the norm")
+    if gate and (x is None or x.dtype != out.dtype or x.stride(-1) != 1):
+        raise KernelError("scan_finish: the gate's rows come in the dtype of out")
+    kernel("recurrence", "gg_scan_finish")(
+        _p(raw), _p(x), dtype_code(out.dtype), x.stride(0) if x is not None else 0, int(g_off), _p(out), _p(weight),
+        _p(seq_of_token), int(n_tokens), int(heads), int(dv), float(eps), float(out_scale), int(whole), int(gate), _stream())
+
+
 # ------------------------------------------------------------------------------- routed experts
 def moe_router_logits(h: torch.Tensor, wr: torch.Tensor, z: torch.Tensor, n_tokens: int) -> None:
     """z[t, e] = wr[e] . h[t], float32 sums on the CUDA cores (the router is never computed in reduced precision)."""
@@ -346,13 +447,19 @@ def moe_router_logits(h: torch.Tensor, wr: torch.Tensor, z: torch.Tensor, n_toke
 
 
 def moe_route(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, seq_of_token: Optional[torch.Tensor],
-              softmax: bool = False, renormalize: bool = False, rows: Optional[int] = None) -> None:
+              softmax: bool = False, renormalize: bool = False, rows: Optional[int] = None,
+              correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1) -> None:
+    """The `top` experts of every row of z and their weights.  correction (float32 [E], optional) is added to the
+    scores for the choice only; with groups > 1 the experts form that many equal runs of neighbours and only the
+    `keep` groups whose two best choice scores sum highest can be chosen from."""
     _need(z, torch.float32, "router logits")
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
     _need(idx, torch.int32, "idx")
     _need(wts, torch.float32, "wts")
     T = z.shape[0] if rows is None else rows
-    kernel("moe", "gg_moe_route")(_p(z), T, z.shape[-1], int(top), int(softmax), int(renormalize), _p(idx), _p(wts),
-                                   _p(seq_of_token), _stream())
+    kernel("moe", "gg_moe_route")(_p(z), T, z.shape[-1], int(top), int(softmax), int(renormalize), _p(correction),
+                                   int(groups), int(keep), _p(idx), _p(wts), _p(seq_of_token), _stream())
 
 
 def moe_gate_up(h: torch.Tensor, w_gu: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, y: torch.Tensor,

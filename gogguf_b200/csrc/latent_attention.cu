@@ -95,7 +95,7 @@ GG_API gg_latent_prep(const void* q, long long ldq, const void* dkv, long long l
                       void* pool, int pool_row, void* qcat, int q_dtype, int ntok, int H, int d, int r, int R,
                       void* dense, int* status, cudaStream_t stream) {
     if (ntok <= 0) return 0;
-    if (H <= 0 || d <= 0 || r <= 0 || R <= 0 || dims < 0 || dims > r || (dims & 1) || pool_row < R + r || page_size <= 0)
+    if (H <= 0 || d <= 0 || r < 0 || R <= 0 || dims < 0 || dims > r || (dims & 1) || pool_row < R + r || page_size <= 0)
         return GG_ERR_ARG;
     const PageBounds pb{n_pages, status};
 #define GG_PREP(T, TQ) gg_launch(latent_prep_kernel<T, TQ>, dim3(ntok), dim3(256), 0, stream, 1, (const T*)q, ldq, \
@@ -209,7 +209,7 @@ template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attention_plain_kernel(
     const TQ* qcat, const TC* pool, int pool_row, TO* out, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int max_pages, int page_size,
-    int H, int R, int r, float scale, int window, const PageBounds pb) {
+    int H, int R, int r, float scale, int window, const PageBounds pb, const float* __restrict__ sink) {
     pdl_launch();
     pdl_wait();
     extern __shared__ float sm[];
@@ -262,12 +262,14 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attention_plain_kernel(
     __syncthreads();
     float Mx = -INFINITY;
     for (int w = 0; w < LAT_WARPS; ++w) Mx = fmaxf(Mx, ml[w * 2]);
+    if (sink != nullptr) Mx = fmaxf(Mx, sink[h]);
     float L = 0.f;
     float f[LAT_WARPS];
     for (int w = 0; w < LAT_WARPS; ++w) {
         f[w] = ml[w * 2] == -INFINITY ? 0.f : expf(ml[w * 2] - Mx);
         L += ml[w * 2 + 1] * f[w];
     }
+    if (sink != nullptr) L += expf(sink[h] - Mx);         // the sink: one more term of the denominator, no value
     const float inv = 1.0f / L;
     for (int i = threadIdx.x; i < R; i += blockDim.x) {
         float s = 0.f;
@@ -280,7 +282,7 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attention_plain_kernel(
 GG_API gg_latent_attention_plain(const void* qcat, int q_dtype, const void* pool, int c_dtype, int pool_row, void* out,
                                  int o_dtype, const int* positions, const int* seq_of_token, const int* page_table,
                                  int max_pages, int page_size, int n_pages, int ntok, int H, int R, int r, float scale,
-                                 int window, int* status, cudaStream_t stream) {
+                                 int window, const float* sink, int* status, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (H <= 0 || H > 65535 || R <= 0 || R > LAT_MAXR || r < 0 || pool_row < R + r || page_size <= 0) return GG_ERR_ARG;
     const size_t smem = ((size_t)(R + r) + (size_t)LAT_WARPS * R + 2 * LAT_WARPS) * sizeof(float);
@@ -289,7 +291,7 @@ GG_API gg_latent_attention_plain(const void* qcat, int q_dtype, const void* pool
     dim3 grid(ntok, H);
 #define GG_LAP(TQ, TC, TO) gg_launch(latent_attention_plain_kernel<TQ, TC, TO>, dim3(grid), dim3(LAT_WARPS * 32), smem, \
         stream, 1, (const TQ*)qcat, (const TC*)pool, pool_row, (TO*)out, positions, seq_of_token, page_table, max_pages, \
-        page_size, H, R, r, scale, window, pb)
+        page_size, H, R, r, scale, window, pb, sink)
     if (q_dtype == GG_F32 && c_dtype == GG_F32 && o_dtype == GG_F32) GG_LAP(float, float, float);
     else if (q_dtype == GG_F32 && c_dtype == GG_BF16 && o_dtype == GG_F32) GG_LAP(float, bf16, float);
     else if (q_dtype == GG_BF16 && c_dtype == GG_BF16 && o_dtype == GG_BF16) GG_LAP(bf16, bf16, bf16);
@@ -414,7 +416,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const bf16* qcat, const bf16* pool, int pool_row, bf16* out, const int* __restrict__ cu_seqlens,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
     int max_pages, int page_size, int n_seqs, int H, int R, int r, float scale_log2, int window, const PageBounds pb,
-    float* part_o, float* part_ml, int q_rows) {
+    float* part_o, float* part_ml, int q_rows, const float* __restrict__ sink) {
     pdl_launch();
     extern __shared__ __align__(16) unsigned char smraw[];
     const int D = R + r, LD = D + 8;
@@ -621,6 +623,8 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!valid[i]) continue;
+        if (sink != nullptr)             // the sink joins the denominator (scores are in log2 units here)
+            lrow[i] += exp2f(sink[(f0 + warp * 16 + g + 8 * i) % H] * 1.4426950408889634f - mrow[i]);
         const float inv = 1.0f / lrow[i];
         bf16* orow = orow0 + (size_t)(warp * 16 + g + 8 * i) * R + z0;
 #pragma unroll
@@ -636,7 +640,8 @@ template <int KT, int RC>
 static int launch_latent_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
                              const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                              int page_size, int n_seqs, int ntok, int H, int R, int r, float scale, int window,
-                             const PageBounds pb, int splits, float* part_o, float* part_ml, int q_rows, cudaStream_t stream) {
+                             const PageBounds pb, int splits, float* part_o, float* part_ml, int q_rows, const float* sink,
+                             cudaStream_t stream) {
     const size_t smem = (size_t)(q_rows + 2 * KT) * (R + r + 8) * sizeof(bf16);
     auto kern = latent_attention_mma_kernel<KT, RC>;
     static bool attr_set = false;                        // per instantiation
@@ -649,12 +654,13 @@ static int launch_latent_mma(const void* qcat, const void* pool, int pool_row, v
     dim3 grid((unsigned)chunks, (R + RC - 1) / RC, splits);
     return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qcat, (const bf16*)pool, pool_row,
                      (bf16*)out, cu_seqlens, positions, seq_of_token, page_table, max_pages, page_size, n_seqs, H, R, r,
-                     scale * 1.4426950408889634f, window, pb, part_o, part_ml, q_rows);
+                     scale * 1.4426950408889634f, window, pb, part_o, part_ml, q_rows, sink);
 }
 
 // Merge of the partial results of a split: one block per (token, head) row.
 __global__ void __launch_bounds__(128) latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out,
-                                                             const int* __restrict__ seq_of_token, int H, int R, int splits) {
+                                                             const int* __restrict__ seq_of_token, int H, int R, int splits,
+                                                             const float* __restrict__ sink) {
     pdl_launch();
     pdl_wait();
     const size_t row = blockIdx.x;
@@ -662,7 +668,9 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(const float* part_o
     const float* ml = part_ml + row * splits * 2;
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
+    const float sk = sink != nullptr ? sink[row % H] * 1.4426950408889634f : -INFINITY;
+    M = fmaxf(M, sk);
+    float L = sink != nullptr ? exp2f(sk - M) : 0.f;
     for (int s = 0; s < splits; ++s) L += ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M) * ml[2 * s + 1];
     const float inv = 1.0f / L;
     for (int c = threadIdx.x; c < R; c += blockDim.x) {
@@ -710,8 +718,8 @@ GG_API gg_latent_attention_mma_takes(int R, int r) {
 GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
                                const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                                int page_size, int n_pages, int n_seqs, int ntok, int H, int R, int r, float scale,
-                               int window, int splits, float* part_o, float* part_ml, int max_new, int* status,
-                               cudaStream_t stream) {
+                               int window, int splits, float* part_o, float* part_ml, int max_new, const float* sink,
+                               int* status, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (!gg_latent_attention_mma_takes(R, r) || H <= 0 || (pool_row % 8) || pool_row < R + r || page_size <= 0 ||
         (page_size % 64) || (((uintptr_t)qcat | (uintptr_t)pool | (uintptr_t)out) & 15))
@@ -719,7 +727,7 @@ GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row,
     const PageBounds pb{n_pages, status};
     const bool wide = (size_t)(64 + 2 * 64) * (R + r + 8) * sizeof(bf16) <= 200 * 1024;     // room for 64-key tiles
 #define GG_LM(KT, RC) launch_latent_mma<KT, RC>(qcat, pool, pool_row, out, cu_seqlens, positions, seq_of_token, page_table, \
-        max_pages, page_size, n_seqs, ntok, H, R, r, scale, window, pb, splits, part_o, part_ml, q_rows, stream)
+        max_pages, page_size, n_seqs, ntok, H, R, r, scale, window, pb, splits, part_o, part_ml, q_rows, sink, stream)
     if (splits < 1 || (splits > 1 && (part_o == nullptr || part_ml == nullptr)) || max_new < 1) return GG_ERR_ARG;
     // the most rows one CTA can have: 64, or all (token, head) pairs of the longest new stretch if those are fewer
     const long long most = (long long)max_new * H;
@@ -731,7 +739,7 @@ GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row,
 #undef GG_LM
     if (rc != 0 || splits == 1) return rc;
     return gg_launch(latent_combine_kernel, dim3((unsigned)(ntok * H)), dim3(128), 0, stream, 1, (const float*)part_o,
-                     (const float*)part_ml, (bf16*)out, seq_of_token, H, R, splits);
+                     (const float*)part_ml, (bf16*)out, seq_of_token, H, R, splits, sink);
 }
 
 // ----------------------------------------------------------------------------- attention of whole prompts, expanded
@@ -746,7 +754,7 @@ template <int DVT>
 __global__ void __launch_bounds__(128) latent_prompt_mma_kernel(
     const bf16* qd, long long ldq, const bf16* qcat, const bf16* kv, long long ldkv, const bf16* ckr, long long ldc,
     bf16* av, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token, int n_seqs, int H, int d, int r,
-    int dv, int R, float scale_log2, int window, float out_scale) {
+    int dv, int R, float scale_log2, int window, float out_scale, const float* __restrict__ sink) {
     pdl_launch();
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr int KT = 64;
@@ -919,6 +927,7 @@ __global__ void __launch_bounds__(128) latent_prompt_mma_kernel(
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!valid[i]) continue;
+        if (sink != nullptr) lrow[i] += exp2f(sink[h] * 1.4426950408889634f - mrow[i]);
         const float inv = out_scale / lrow[i];
         bf16* orow = av + ((size_t)(t0 + prow[i]) * H + h) * dv;
 #pragma unroll
@@ -932,7 +941,7 @@ __global__ void __launch_bounds__(128) latent_prompt_mma_kernel(
 // Does the expanded prompt kernel take these sizes?  Plain, rotated and value sizes whose rows and split points fall
 // on 16-byte boundaries, d + r and dv multiples of 16, dv at most 128, d + r at most 256.
 GG_API gg_latent_prompt_mma_takes(int d, int r, int dv) {
-    return (d > 0 && r > 0 && dv > 0 && d % 8 == 0 && r % 8 == 0 && (d + r) % 16 == 0 && dv % 16 == 0 && dv <= 128 &&
+    return (d > 0 && r >= 0 && dv > 0 && d % 8 == 0 && r % 8 == 0 && (d + r) % 16 == 0 && dv % 16 == 0 && dv <= 128 &&
             d + r <= 256) ? 1 : 0;
 }
 
@@ -942,7 +951,7 @@ GG_API gg_latent_prompt_mma_takes(int d, int r, int dv) {
 GG_API gg_latent_prompt_mma(const void* qd, long long ldq, const void* qcat, const void* kv, long long ldkv,
                             const void* ckr, long long ldc, void* av, const int* cu_seqlens, const int* seq_of_token,
                             int n_seqs, int ntok, int H, int d, int r, int dv, int R, float scale, int window,
-                            float out_scale, cudaStream_t stream) {
+                            float out_scale, const float* sink, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (!gg_latent_prompt_mma_takes(d, r, dv) || H <= 0 || H > 65535 || (ldq % 8) || (ldkv % 8) || (ldc % 8) ||
         ((R + r) % 8) || (R % 8) || ((H * d) % 8) ||
@@ -961,7 +970,7 @@ GG_API gg_latent_prompt_mma(const void* qd, long long ldq, const void* qcat, con
         }
         return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qd, ldq, (const bf16*)qcat, (const bf16*)kv,
                          ldkv, (const bf16*)ckr, ldc, (bf16*)av, cu_seqlens, seq_of_token, n_seqs, H, d, r, dv, R, sl2, window,
-                         out_scale);
+                         out_scale, sink);
     }
     auto kern = latent_prompt_mma_kernel<128>;
     static bool set2 = false;
@@ -971,7 +980,7 @@ GG_API gg_latent_prompt_mma(const void* qd, long long ldq, const void* qcat, con
         set2 = true;
     }
     return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qd, ldq, (const bf16*)qcat, (const bf16*)kv, ldkv,
-                     (const bf16*)ckr, ldc, (bf16*)av, cu_seqlens, seq_of_token, n_seqs, H, d, r, dv, R, sl2, window, out_scale);
+                     (const bf16*)ckr, ldc, (bf16*)av, cu_seqlens, seq_of_token, n_seqs, H, d, r, dv, R, sl2, window, out_scale, sink);
 }
 
 GG_API gg_latent_attention_checked() { return gg_debug_bounds(); }

@@ -101,11 +101,112 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const float* z, int E, in
     }
 }
 
-GG_API gg_moe_route(const float* z, int T, int E, int top, int softmax, int renorm, int* idx, float* wts,
-                    const int* seq_of_token, cudaStream_t stream) {
+// The same choice with a correction and groups: scores s = sigmoid(z) (or softmax); the choice scores are
+// s + correction[e] (correction may be null); the experts form `groups` equal runs of neighbours, a group's score
+// is the sum of its two largest choice scores, and only experts of the `keep` best groups can be chosen (the others
+// count as minus infinity).  The `top` largest choice scores are chosen (ties to the lower index); the weights are
+// the chosen experts' scores s without the correction.  One warp per token; scores in shared memory.
+__global__ void __launch_bounds__(32) moe_route_grouped_kernel(const float* z, int E, int top, int softmax, int renorm,
+                                                               const float* __restrict__ correction, int groups, int keep,
+                                                               int* idx, float* wts, const int* __restrict__ seq_of_token) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float rsm[];
+    float* sc = rsm;                 // [E] scores
+    float* ch = sc + E;              // [E] choice scores (minus infinity once chosen or outside the kept groups)
+    float* gsc = ch + E;             // [groups]
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float* zt = z + (size_t)t * E;
+    if (seq_of_token != nullptr && seq_of_token[t] < 0) {      // padding: expert 0 with weight 0
+        for (int k = lane; k < top; k += 32) { idx[(size_t)t * top + k] = 0; wts[(size_t)t * top + k] = 0.f; }
+        return;
+    }
+    float mx = -INFINITY, den = 1.f;
+    if (softmax) {
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zt[e]);
+        mx = warp_max(mx);
+        float s = 0.f;
+        for (int e = lane; e < E; e += 32) s += expf(zt[e] - mx);
+        den = warp_sum(s);
+    }
+    for (int e = lane; e < E; e += 32) {
+        const float s = softmax ? expf(zt[e] - mx) / den : 1.0f / (1.0f + expf(-zt[e]));
+        sc[e] = s;
+        ch[e] = s + (correction != nullptr ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float a = -INFINITY, b2 = -INFINITY;             // the two largest of the group
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = ch[e];
+                if (v > a) { b2 = a; a = v; } else if (v > b2) b2 = v;
+            }
+            gsc[g] = per > 1 ? a + b2 : a;
+        }
+        __syncwarp();
+        // drop the groups - keep worst groups: the worst is the lowest score, ties to the higher index
+        for (int k = 0; k < groups - keep; ++k) {
+            float wv = INFINITY;
+            int wi = -1;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gsc[g];
+                if (v != INFINITY && (v < wv || (v == wv && g > wi))) { wv = v; wi = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+                if (oi >= 0 && (wi < 0 || ov < wv || (ov == wv && oi > wi))) { wv = ov; wi = oi; }
+            }
+            if (wi < 0) break;
+            for (int e = wi * per + lane; e < (wi + 1) * per; e += 32) ch[e] = -INFINITY;
+            if (lane == 0) gsc[wi] = INFINITY;                // marks a dropped group
+            __syncwarp();
+        }
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = ch[e];
+            if (v > bv || (v == bv && e < bi && v != -INFINITY)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi >= E) bi = 0;                                  // fewer candidates than `top` (refused by the launcher)
+        const float s = sc[bi];
+        if (lane == 0) { idx[(size_t)t * top + k] = bi; wts[(size_t)t * top + k] = bv == -INFINITY ? 0.f : s; ch[bi] = -INFINITY; }
+        total += s;
+        __syncwarp();
+    }
+    if (renorm) {
+        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] /= total;
+    }
+}
+
+// correction [E] (may be null); groups >= 1 equal runs of neighbouring experts of which `keep` can be chosen from.
+GG_API gg_moe_route(const float* z, int T, int E, int top, int softmax, int renorm, const float* correction, int groups,
+                    int keep, int* idx, float* wts, const int* seq_of_token, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E) return GG_ERR_ARG;
-    gg_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, 1, z, E, top, softmax, renorm, idx, wts, seq_of_token);
+    if (groups < 1) groups = 1;
+    if (keep < 1 || keep > groups) keep = groups;
+    if (correction == nullptr && keep == groups) {
+        gg_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, 1, z, E, top, softmax, renorm, idx, wts, seq_of_token);
+        return gg_last_error();
+    }
+    if (E % groups || top > (E / groups) * keep) return GG_ERR_ARG;
+    const size_t smem = ((size_t)2 * E + groups) * sizeof(float);
+    if (smem > 48 * 1024) return GG_ERR_ARG;
+    gg_launch(moe_route_grouped_kernel, dim3(T), dim3(32), smem, stream, 1, z, E, top, softmax, renorm, correction, groups,
+              keep, idx, wts, seq_of_token);
     return gg_last_error();
 }
 

@@ -103,11 +103,16 @@ class SandwichNormBlock:
     """A norm on either side of each part: x += post1(mixer(pre1(x))); x += post2(feed_forward(pre2(x))).  The
     feed-forward (with its two norms) may be absent.  A part's output is collected in a zeroed float32 buffer;
     the norm after the part and the add into the residual stream are one kernel, all in float32.  The norms
-    after the parts must be of the form y / rms(y) * weight (they expose `weight` and `eps`)."""
+    after the parts must be of the form y / rms(y) * weight (they expose `weight` and `eps`).
+
+    A part may have a gate (roles mixer_gate, feed_forward_gate): the part's output is multiplied, element by
+    element, by sigmoid(gate.logits(h) + gate.bias), h being the normed rows the part is handed, before the norm
+    after the part: x += post(part(pre(x)) * gate(pre(x))).  The multiplication is done by the norm-and-add kernel."""
 
     roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "mixer_post_norm": "norm",
-             "feed_forward_norm": "norm", "feed_forward_post_norm": "norm"}
-    optional_roles = ("feed_forward", "feed_forward_norm", "feed_forward_post_norm")
+             "feed_forward_norm": "norm", "feed_forward_post_norm": "norm", "mixer_gate": "gate",
+             "feed_forward_gate": "gate"}
+    optional_roles = ("feed_forward", "feed_forward_norm", "feed_forward_post_norm", "mixer_gate", "feed_forward_gate")
     keeps_row_stats = True      # its statistics are its own (see `forward`); it clears and sets `fresh` itself
     STATS = "sandwich_row_stats"
     ZEROED = "block_part_out_zeroed"      # ctx.shared: address of the parts' output buffer while it is known to hold zeros
@@ -118,6 +123,9 @@ class SandwichNormBlock:
         self.mixer, self.mixer_norm, self.mixer_post = parts["mixer"], parts["mixer_norm"], parts["mixer_post_norm"]
         self.feed_forward = parts.get("feed_forward")
         self.ff_norm, self.ff_post = parts.get("feed_forward_norm"), parts.get("feed_forward_post_norm")
+        self.mixer_gate, self.ff_gate = parts.get("mixer_gate"), parts.get("feed_forward_gate")
+        if self.ff_gate is not None and self.feed_forward is None:
+            raise ValueError("sandwich_norm: a feed_forward_gate without a feed-forward")
         if self.feed_forward is not None and (self.ff_norm is None or self.ff_post is None):
             raise ValueError("sandwich_norm: a feed-forward needs feed_forward_norm and feed_forward_post_norm")
         for post in (self.mixer_post, self.ff_post):
@@ -125,11 +133,14 @@ class SandwichNormBlock:
                 raise ValueError("sandwich_norm: the norm after a part must be y / rms(y) * weight")
         # A part may take the norm before it into its first projection (`absorb_norm(norm) -> bool`); it then reads
         # the residual's RowStats, which the norm-and-add kernel of the part before it has left behind.
-        self.mixer_folded = _offer_norm(self.mixer, self.mixer_norm, rt)
-        self.ff_folded = self.feed_forward is not None and _offer_norm(self.feed_forward, self.ff_norm, rt)
+        # (a gated part is handed the normed rows themselves: its gate reads them too)
+        self.mixer_folded = self.mixer_gate is None and _offer_norm(self.mixer, self.mixer_norm, rt)
+        self.ff_folded = (self.feed_forward is not None and self.ff_gate is None
+                          and _offer_norm(self.feed_forward, self.ff_norm, rt))
         self.any_folded = self.mixer_folded or self.ff_folded
 
-    def _part(self, x: torch.Tensor, ctx: StepContext, pre, post, call, folded: bool, stats, emit: bool) -> None:
+    def _part(self, x: torch.Tensor, ctx: StepContext, pre, post, call, folded: bool, stats, emit: bool,
+              gate=None) -> None:
         if folded:
             h = stats.ensure(x)
         else:
@@ -140,12 +151,14 @@ class SandwichNormBlock:
         # (or one that follows a block of another make, which says so by dropping the mark) pays for a fill
         if ctx.shared.get(self.ZEROED) != y.data_ptr():
             y.zero_()
+        g = gate.logits(h, ctx) if gate is not None else None
+        gb = gate.bias if gate is not None else None
         call(h, y)
         if stats is not None and emit:
-            K.rmsnorm_add(x, y, post.weight, post.eps, xhat=stats.xhat, ssq=stats.ssq, zero_y=True)
+            K.rmsnorm_add(x, y, post.weight, post.eps, xhat=stats.xhat, ssq=stats.ssq, zero_y=True, gate=g, gate_bias=gb)
             stats.fresh = True
         else:
-            K.rmsnorm_add(x, y, post.weight, post.eps, zero_y=True)
+            K.rmsnorm_add(x, y, post.weight, post.eps, zero_y=True, gate=g, gate_bias=gb)
             if stats is not None:
                 stats.fresh = False
         ctx.shared[self.ZEROED] = y.data_ptr()
@@ -163,10 +176,10 @@ class SandwichNormBlock:
         # folded; across blocks it always does (the next block may be of another make: it re-makes what is stale)
         self._part(x, ctx, self.mixer_norm, self.mixer_post,
                    lambda h, y: self.mixer.forward(h, y, ctx, cache, writes_cache), self.mixer_folded, stats,
-                   emit=self.feed_forward is None or self.ff_folded)
+                   emit=self.feed_forward is None or self.ff_folded, gate=self.mixer_gate)
         if self.feed_forward is not None:
             self._part(x, ctx, self.ff_norm, self.ff_post, lambda h, y: self.feed_forward.forward(h, y, ctx),
-                       self.ff_folded, stats, emit=True)
+                       self.ff_folded, stats, emit=True, gate=self.ff_gate)
 
 
 def _offer_norm(part, norm, rt: Runtime) -> bool:

@@ -14,8 +14,9 @@ from .registry import register_embedding, register_head
 
 @register_embedding("embedding")
 class TokenEmbedding:
-    """x = E[token]: a row gather into the float32 residual stream, no scaling
-    (pkg/model/qwen3/model.go:169-196).  ``tensor`` of the spec names the stored table (default "weight")."""
+    """x = E[token]: a row gather into the float32 residual stream (pkg/model/qwen3/model.go:169-196).  ``tensor``
+    of the spec names the stored table (default "weight"); ``scale`` (default 1) multiplies the gathered rows in
+    float32 (the table itself stays as stored, also for a head that is tied to it)."""
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -24,16 +25,18 @@ class TokenEmbedding:
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
         self.weight = rt.matrix(weights[spec.get("tensor", "weight")])
+        self.scale = float(spec.get("scale", 1.0))
 
     def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> None:
-        K.embed_gather(self.weight, tokens, out)
+        K.embed_gather(self.weight, tokens, out, self.scale)
 
 
 @register_head("linear_head")
 class LinearHead:
     """logits = W h in float32; W is the embedding matrix when the spec says `tied_to`
     (pkg/model/qwen3/model.go:578-610, pkg/model/qwen3/tensors.go:36-48).  ``tensor`` of the spec names the
-    stored matrix under the part's prefix (default "weight")."""
+    stored matrix under the part's prefix (default "weight").  ``softcap`` (optional, c > 0): the logits are
+    bounded smoothly, c tanh(logits / c), in float32."""
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -43,6 +46,10 @@ class LinearHead:
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime,
                  tied: Optional[torch.Tensor] = None):
         self.vocab = int(spec["vocab_size"])
+        cap = spec.get("softcap")
+        self.softcap = float(cap) if cap else 0.0
+        if self.softcap < 0.0:
+            raise ValueError("head: softcap must be positive")
         if spec.get("tied_to") is not None:
             if tied is None:
                 raise ValueError("head is tied but no embedding matrix was given")
@@ -52,3 +59,6 @@ class LinearHead:
 
     def forward(self, h: torch.Tensor, logits: torch.Tensor, ctx: StepContext, m: Optional[int] = None) -> None:
         self.proj(h, logits, m=m, ws=ctx.ws)
+        if self.softcap:
+            rows = logits.shape[0] if m is None else m
+            K.softcap(logits, self.softcap, rows * self.vocab)

@@ -5,7 +5,9 @@ a_p = softplus(p), a_q = 1/2 + softplus(q); the stored tensor `act` holds (p, q)
 
 Routed experts (`routed_experts`): router logits W_r h in float32, scores by sigmoid (or softmax), the `top_k`
 largest chosen, weights the chosen scores (optionally renormalised), the weight applied to the expert's input
-or to its output.  An expert is a gated unit: y = act(Wg x, Wu x), out = Wd y, with
+or to its output.  `correction` (a stored vector, named in `names`) is added to the scores for the choice only, the
+weights stay the scores themselves; `groups` {count, keep}: the experts form `count` equal runs of neighbours, a
+group's score is the sum of its two largest choice scores, and only experts of the `keep` best groups can be chosen.  An expert is a gated unit: y = act(Wg x, Wu x), out = Wd y, with
 act "clamped_glu": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + up_offset)
 (up_offset 1 unless given); act "silu_glu": silu(g) u, the same unit without a limit, with slope 1 and offset 0.
 `shared` (optional: intermediate_size, prefix, names) adds one dense gated unit that every token runs
@@ -79,7 +81,7 @@ class RoutedExperts:
     @classmethod
     def _names(cls, spec: PartSpec) -> Dict[str, str]:
         n = dict(router="router.weight", expert="experts.{}.", gate="gate_proj.weight", up="up_proj.weight",
-                 down="down_proj.weight")
+                 down="down_proj.weight", correction="router.correction")
         n.update(spec.get("names") or {})
         return n
 
@@ -88,6 +90,8 @@ class RoutedExperts:
         h, i, E = spec["hidden_size"], spec["intermediate_size"], spec["num_experts"]
         n = cls._names(spec)
         t = {n["router"]: TensorDecl(shape=(E, h))}
+        if spec.get("correction"):
+            t[n["correction"]] = TensorDecl(shape=(E,), init="small_normal")
         for e in range(E):
             p = n["expert"].format(e)
             t[p + n["gate"]] = TensorDecl(shape=(i, h))
@@ -135,6 +139,15 @@ class RoutedExperts:
             raise ValueError(f"routed experts: unknown activation {kind!r} (clamped_glu, silu_glu)")
         n = self._names(spec)
         self.router_w = rt.matrix(weights[n["router"]])
+        self.correction = rt.vector(weights[n["correction"]]) if spec.get("correction") else None
+        gr = dict(spec.get("groups") or {})
+        self.groups = int(gr.get("count", 1))
+        self.keep = int(gr.get("keep", self.groups))
+        if self.groups < 1 or self.E % self.groups or not (1 <= self.keep <= self.groups):
+            raise ValueError(f"routed experts: {self.E} experts do not form {self.groups} equal groups of which "
+                             f"{self.keep} are kept")
+        if self.top > (self.E // self.groups) * self.keep:
+            raise ValueError(f"routed experts: top_k={self.top} exceeds the experts of the {self.keep} kept groups")
         gu: List[torch.Tensor] = []
         dn: List[torch.Tensor] = []
         for e in range(self.E):
@@ -176,7 +189,8 @@ class RoutedExperts:
         K.moe_router_logits(h, self.router_w, z, T)      # CUDA cores, float32 sums: the router is never reduced
         idx = ctx.ws.get("moe_idx", (T, self.top), torch.int32)
         wts = ctx.ws.get("moe_wts", (T, self.top), torch.float32)
-        K.moe_route(z, self.top, idx, wts, ctx.seq_of_token, softmax=self.softmax, renormalize=self.renorm, rows=T)
+        K.moe_route(z, self.top, idx, wts, ctx.seq_of_token, softmax=self.softmax, renormalize=self.renorm, rows=T,
+                    correction=self.correction, groups=self.groups, keep=self.keep)
         return idx, wts
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:

@@ -18,8 +18,16 @@ compute the same sums, so a position's result does not depend on how its sequenc
 rounding.
 
 The rotation is the adjacent-pair kind (`rope_adjacent`), applied to the first `rotary_dim` elements of the
-rot part.  Spec parameters: hidden_size, num_heads, nope_dim, rope_dim, value_dim, latent_dim, scale, window,
-latent_norm_eps, position, and optionally `names` (local tensor names of q, down, latent_norm, up_k, up_v, out).
+rot part; `rope_dim` may be 0 (no rotated part, no position encoding: `position` is then left out).
+
+Two options.  `q_latent_dim` (Rq): the queries go through a latent of their own, c_q = N(W_dq h; w_q) (RMS norm with
+a plain weight, `latent_norm_eps`), q = W_uq c_q; W_dq and the key/value down projection run as one product.
+`sink`: a stored number per head whose exponential joins the softmax's denominator; it has no key and no value, is
+not scaled, and counts once.
+
+Spec parameters: hidden_size, num_heads, nope_dim, rope_dim, value_dim, latent_dim, scale, window,
+latent_norm_eps, position, q_latent_dim, sink, and optionally `names` (local tensor names of q, down, latent_norm,
+up_k, up_v, out; with a query latent q_down, q_latent_norm and q (the up projection); with a sink, sink).
 """
 from __future__ import annotations
 
@@ -37,7 +45,8 @@ from .registry import POSITIONS, lookup, register_mixer
 PROMPT_FORM_MIN_TOKENS = 32      # whole prompts of at least this many tokens take the expanded form
 
 _NAMES = dict(q="q_proj.weight", down="kv_down_proj.weight", latent_norm="kv_norm.weight", up_k="k_up_proj.weight",
-              up_v="v_up_proj.weight", out="o_proj.weight")
+              up_v="v_up_proj.weight", out="o_proj.weight", q_down="q_down_proj.weight", q_latent_norm="q_norm.weight",
+              sink="sink")
 
 
 def _names(spec: PartSpec) -> Dict[str, str]:
@@ -53,8 +62,16 @@ class LatentAttentionMixer:
         W, H = spec["hidden_size"], spec["num_heads"]
         d, r, dv, R = spec["nope_dim"], spec["rope_dim"], spec["value_dim"], spec["latent_dim"]
         n = _names(spec)
+        Rq = int(spec.get("q_latent_dim") or 0)
+        extra = {}
+        if Rq:
+            extra[n["q_down"]] = TensorDecl(shape=(Rq, W))
+            extra[n["q_latent_norm"]] = TensorDecl(shape=(Rq,), init="ones_normal")
+        if spec.get("sink"):
+            extra[n["sink"]] = TensorDecl(shape=(H,), init="small_normal")
         return {
-            n["q"]: TensorDecl(shape=(H * (d + r), W)),
+            **extra,
+            n["q"]: TensorDecl(shape=(H * (d + r), Rq or W)),
             n["down"]: TensorDecl(shape=(R + r, W)),
             n["latent_norm"]: TensorDecl(shape=(R,), init="ones_normal"),
             n["up_k"]: TensorDecl(shape=(H * d, R)),
@@ -74,21 +91,31 @@ class LatentAttentionMixer:
         self.scale = float(spec["scale"])
         self.window = int(spec.get("window") or 0)
         self.eps = float(spec["latent_norm_eps"])
-        pos = dict(spec["position"])
-        self.position = lookup(POSITIONS, pos["kind"], "position encoding")(pos, rt)
-        if getattr(self.position, "pairing", None) != "adjacent":
-            raise ValueError("latent attention rotates adjacent pairs; its position encoding must be of that kind")
-        self.rot = int(pos.get("rotary_dim", self.r))
-        if self.rot > self.r or self.rot % 2:
-            raise ValueError(f"latent attention: rotary_dim={self.rot} must be even and at most rope_dim={self.r}")
+        self.position = None
+        self.rot = 0
+        if self.r > 0:
+            pos = dict(spec["position"])
+            self.position = lookup(POSITIONS, pos["kind"], "position encoding")(pos, rt)
+            if getattr(self.position, "pairing", None) != "adjacent":
+                raise ValueError("latent attention rotates adjacent pairs; its position encoding must be of that kind")
+            self.rot = int(pos.get("rotary_dim", self.r))
+            if self.rot > self.r or self.rot % 2:
+                raise ValueError(f"latent attention: rotary_dim={self.rot} must be even and at most rope_dim={self.r}")
         n = _names(spec)
         H, d, r, dv, R = self.H, self.d, self.r, self.dv, self.R
-        wq, wdown = rt.matrix(weights[n["q"]]), rt.matrix(weights[n["down"]])
+        self.Rq = int(spec.get("q_latent_dim") or 0)
+        # with a query latent the first product makes [query latent | latent | key part] and the queries follow
+        # from the normed query latent by a product of their own
+        wq = rt.matrix(weights[n["q_down"] if self.Rq else n["q"]])
+        wdown = rt.matrix(weights[n["down"]])
         if wq.dtype != wdown.dtype:
             wq, wdown = wq.float(), wdown.float()
         # one product for the queries and the down projection: rows [all q heads | latent | shared key part]
         self.q_down = Linear(torch.cat([wq, wdown], dim=0), rt)
-        self.nq = H * (d + r)
+        self.nq = self.Rq or H * (d + r)
+        self.q_up = Linear(weights[n["q"]], rt) if self.Rq else None
+        self.q_latent_norm = rt.vector(weights[n["q_latent_norm"]]) if self.Rq else None
+        self.sink = rt.vector(weights[n["sink"]]) if spec.get("sink") else None
         self.latent_norm = rt.vector(weights[n["latent_norm"]])
         # per head: Wuk_h^T as [latent_dim, nope_dim] (the absorbed query is Wuk_h^T q_plain), Wuv_h as stored
         self.uk_t = rt.matrix(weights[n["up_k"]]).view(H, d, R).transpose(1, 2).contiguous()
@@ -99,7 +126,8 @@ class LatentAttentionMixer:
         self.kv_up = None
         if rt.fast and rt.dtype == torch.bfloat16 and self.uk_t.dtype == torch.bfloat16:
             from ..csrc import fast_latent
-            self._fast = fast_latent.try_make(H, d, R, r, self.nq + R + r, self.scale, self.window)
+            self._fast = fast_latent.try_make(H, d, R, r, H * (d + r) if self.Rq else self.nq + R + r, self.scale,
+                                              self.window, self.sink)
             # whole prompts: keys and values of all heads by one product, attention in the expanded form
             if (self._fast is not None and fast_latent.prompt_takes(d, r, dv) and R % 8 == 0 and (H * d) % 8 == 0
                     and (H * dv) % 8 == 0):
@@ -113,7 +141,8 @@ class LatentAttentionMixer:
         return True
 
     def prepare(self, ctx: StepContext) -> None:
-        self.position.tables(ctx)
+        if self.position is not None:
+            self.position.tables(ctx)
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext, cache: LatentView,
                 writes_cache: bool = True) -> None:
@@ -125,24 +154,33 @@ class LatentAttentionMixer:
         width = self.nq + R + r
         qd = ctx.ws.get("lat_q_down", (T, width), dt)
         self.q_down(h, qd, ws=ctx.ws)
+        dkv = qd[:, self.nq:]
+        if self.Rq:
+            # queries through their own latent: norm of the first Rq columns, then the up projection
+            cq = ctx.ws.get("lat_q_latent", (T, self.Rq), dt)
+            K.rmsnorm_rows(qd[:, :self.Rq], self.q_latent_norm, self.eps, cq, T)
+            qd = ctx.ws.get("lat_q_heads", (T, H * (d + r)), dt)
+            self.q_up(cq, qd, ws=ctx.ws)
+            width = H * (d + r)
+        qh = qd[:, :H * (d + r)]
         qcat = ctx.ws.get("lat_qcat", (T, H, R + r), mid)
-        cos, sin = self.position.tables(ctx)
+        cos, sin = self.position.tables(ctx) if self.position is not None else (None, None)
         table = ctx.page_tables[cache.group]
         av = ctx.ws.get("lat_values", (T, H * dv), dt)
         if self.kv_up is not None and ctx.fresh and ctx.max_new >= PROMPT_FORM_MIN_TOKENS:
             # every sequence starts at position 0: what a token reads is among the step's own tokens
             from ..csrc import fast_latent
             ckr = ctx.ws.get("lat_rows_dense", (T, R + r), dt)
-            K.latent_prep(qd[:, :self.nq], qd[:, self.nq:], self.latent_norm, self.eps, cos, sin, self.rot,
+            K.latent_prep(qh, dkv, self.latent_norm, self.eps, cos, sin, self.rot,
                           ctx.positions, ctx.seq_of_token, table, cache.page_size,
                           cache.pool if writes_cache else None, qcat, T, H, d, r, R, dense=ckr)
             kv = ctx.ws.get("lat_keys_values", (T, H * (d + dv)), dt)
             self.kv_up(ckr[:, :R], kv, ws=ctx.ws)
             fast_latent.latent_prompt_mma(qd, qcat, kv, ckr, av, ctx.cu_seqlens, ctx.seq_of_token, ctx.n_seqs, T, H, d, r,
-                                          dv, R, self.scale, self.window, self.out_scale)
+                                          dv, R, self.scale, self.window, self.out_scale, self.sink)
             self.o(av, residual, accumulate=True, ws=ctx.ws)
             return
-        K.latent_prep(qd[:, :self.nq], qd[:, self.nq:], self.latent_norm, self.eps, cos, sin, self.rot,
+        K.latent_prep(qh, dkv, self.latent_norm, self.eps, cos, sin, self.rot,
                       ctx.positions, ctx.seq_of_token, table, cache.page_size, cache.pool if writes_cache else None,
                       qcat, T, H, d, r, R)
         if self._fast is not None:
@@ -154,7 +192,7 @@ class LatentAttentionMixer:
             self._fast.attention(qcat, cache.pool, olat, ctx, table, cache.page_size)
         else:
             K.latent_attention_plain(qcat, cache.pool, olat, ctx.positions, ctx.seq_of_token, table,
-                                     cache.page_size, T, H, R, r, self.scale, self.window)
+                                     cache.page_size, T, H, R, r, self.scale, self.window, self.sink)
         if self._fast is not None:
             self._fast.expand(olat, self.uv, av, T, self.out_scale)
         else:

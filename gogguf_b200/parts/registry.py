@@ -12,6 +12,9 @@ Interfaces (duck-typed; see `gogguf_b200.parts.base` for the step context they r
                 `h[T, hidden]` (compute dtype) and ADDS its output into `residual[T, hidden]` (float32).
 * feed-forward: ``forward(h, residual, ctx)``, same contract.
 * norm:         ``forward(x, out, rows=None)``: `x` float32 rows -> `out` in the compute dtype.
+* gate:         ``logits(h, ctx) -> float32 [T, size]`` (workspace memory, valid until the gate is asked again) and
+                an attribute ``bias`` (float32 [size] or None): what an arrangement multiplies a part's output by,
+                element by element, after a sigmoid of logits + bias.
 * position:     built by the mixer that uses it from ``spec["position"]``; ``tables(ctx)``.
 * arrangement:  class attribute ``roles = {role: family}`` (family "mixer", "feed_forward" or "norm"; optional
                 ``optional_roles``), ``__init__(block_spec, parts, runtime)`` with `parts` the built parts by role,
@@ -26,6 +29,7 @@ from typing import Callable, Dict, Type
 MIXERS: Dict[str, Type] = {}
 FEED_FORWARDS: Dict[str, Type] = {}
 NORMS: Dict[str, Type] = {}
+GATES: Dict[str, Type] = {}
 POSITIONS: Dict[str, Type] = {}
 ARRANGEMENTS: Dict[str, Type] = {}
 EMBEDDINGS: Dict[str, Type] = {}
@@ -46,6 +50,7 @@ def _register(table: Dict[str, Type], what: str) -> Callable[[str], Callable[[Ty
 register_mixer = _register(MIXERS, "mixer")
 register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
+register_gate = _register(GATES, "gate")
 register_position = _register(POSITIONS, "position encoding")
 register_arrangement = _register(ARRANGEMENTS, "block arrangement")
 register_embedding = _register(EMBEDDINGS, "embedding")

@@ -41,7 +41,7 @@ class TensorDecl:
     """What a part expects of one tensor.
 
     init: "normal" (N(0, std)), "ones_normal" (1 + N(0, norm_std)), "zeros_normal" (N(0, norm_std)),
-    "small_normal" (N(0, 0.5)) or "zeros";
+    "small_normal" (N(0, 0.5)), "unit_interval" (sigmoid of N(0, 1): numbers inside (0, 1)) or "zeros";
     used only by the random-weights mode.  optional: may be absent (for
     instance a separate head matrix of a model with tied embeddings).
     """
@@ -162,6 +162,8 @@ def random_tensors(expected: Mapping[str, TensorDecl], seed: int, std: float, no
                 t.mul_(norm_std)
             elif d.init == "small_normal":       # scalars of an activation, around zero
                 t.mul_(0.5)
+            elif d.init == "unit_interval":      # lower bounds of a gate
+                t.sigmoid_()
             else:
                 raise ValueError(f"tensor {name!r}: unknown init {d.init!r}")
         out[name] = t.to(dtype)
