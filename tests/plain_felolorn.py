@@ -13,7 +13,7 @@ Notation: x [n, W] is the residual stream of one sequence, positions are 0..n-1.
     conv(a)_t:  sum_j c[:, j] * a_(t - taps + 1 + j), zero before position 0 (per channel, over time)
     mixer:      latent attention with a sink, lightning attention, or HGRN2
     ff:         routed experts, chosen inside the best groups
-    output:     z = E N(x; w_final);  logits = cap * tanh(z / cap)
+    output:     z = E N(x; w_final);  logits = cap * tanh(z / cap)                      (z itself without a cap)
 """
 from __future__ import annotations
 
@@ -184,11 +184,11 @@ def forward(tokens: List[int], w: Dict[str, torch.Tensor], cfg: dict, dtype=torc
             streams: Optional[list] = None) -> torch.Tensor:
     """Logits [n, vocab] of one sequence; `streams`, if given, receives the residual stream after every layer."""
     E = w["embed"].to(dtype)
-    x = E[torch.tensor(tokens, dtype=torch.long)] * float(cfg["embedding"]["scale"])
+    x = E[torch.tensor(tokens, dtype=torch.long)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     for i in range(len(cfg["layers"])):
         x = layer(x, w, i, cfg)
         if streams is not None:
             streams.append(x.clone())
     z = wnorm(x, w["final.norm"], float(cfg["norm"]["eps"])) @ E.T
-    cap = float(cfg["logit_softcap"])
-    return cap * torch.tanh(z / cap)
+    cap = cfg.get("logit_softcap")
+    return float(cap) * torch.tanh(z / float(cap)) if cap else z
