@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload] [--prefill-lengths 256,1024] [--decode-contexts 16384,32768]
-    python bench.py --compare gigopel|sokirax [--compare-sizes 2k,4k]      (another workload, see the end of this text)
+    python bench.py --compare gigopel|sokirax|felolorn [--compare-sizes 2k,4k]   (another workload, see the end of this text)
 
 A "step" is one decode step of a batch: every sequence goes on by one token, sampled greedily on the
 device.  The timed region is exactly K steps after W warm-up steps, timed with CUDA events on the
@@ -32,6 +32,12 @@ line {"compare": "gigopel", "sizes": {...}} and per-model lines on stderr.
 or windowed attention with sinks beside retention; gated units or routed experts with a shared unit): an all-dense
 and an all-experts model per size, layers alternating between the two mixers, beside the same Qwen3.  It prints
 {"compare": "sokirax", "sizes": {...}}.
+
+`--compare felolorn` measures the Felolorn design (norms on both sides of every part, a gate on every part's
+output, a short convolution before the mixer; latent attention with a query latent and sinks, lightning attention
+or HGRN2; experts chosen inside the best groups): an all-experts model per size whose layers cycle through the three
+mixers, beside the all-experts Sokirax model (its closest relative: the same arrangement of norms, retention,
+routed experts) and the same Qwen3.  It prints {"compare": "felolorn", "sizes": {...}}.
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures of an earlier measurement on this pool.  The weights (16 GB) are far larger than
@@ -209,6 +215,34 @@ def sokirax_config(z, kind):
                         for i in range(z["layers"])])
 
 
+# Felolorn at the same widths and depths: latent attention with Gigopel's head sizes and latent (no rotated part,
+# no window), matrix states of 128 x 128 as Sokirax's retention, the same experts in four groups of which two are kept
+FELOLORN_SIZES = {
+    "2k": dict(width=2048, heads=16, dim=64, vdim=64, kv_rank=256, q_rank=512, state_heads=8, taps=4, experts=16, top=2,
+               groups=4, keep=2, expert_ff=1024, layers=8, vocab=65536),
+    "4k": dict(width=4096, heads=32, dim=128, vdim=128, kv_rank=512, q_rank=1024, state_heads=16, taps=4, experts=32, top=4,
+               groups=4, keep=2, expert_ff=2048, layers=8, vocab=65536),
+}
+
+
+def felolorn_config(z):
+    """Layers cycle through HGRN2, latent attention and lightning attention (heads of 128 x 128, decays from
+    1 - 2^-5 to 1 - 2^-12); every layer has routed experts."""
+    R = z["state_heads"]
+    mixers = [
+        ("hgrn2", dict(heads=R, dim=128, vdim=128)),
+        ("latent_attention", dict(heads=z["heads"], dim=z["dim"], vdim=z["vdim"], kv_rank=z["kv_rank"], q_rank=z["q_rank"],
+                                  scale=z["dim"] ** -0.5)),
+        ("lightning", dict(heads=R, dim=128, vdim=128,
+                           decay=[1.0 - 2.0 ** (-5.0 - 7.0 * i / max(R - 1, 1)) for i in range(R)])),
+    ]
+    mlp = dict(kind="moe", expert=dict(ff=z["expert_ff"]),
+               router=dict(experts=z["experts"], top=z["top"], groups=dict(count=z["groups"], keep=z["keep"])))
+    return dict(architecture="Felolorn", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), initializer_range=0.02,
+                embedding=dict(scale=z["width"] ** 0.5), canon=dict(taps=z["taps"]), logit_softcap=30.0,
+                layers=[dict(type=mixers[i % 3][0], mixer=mixers[i % 3][1], mlp=mlp) for i in range(z["layers"])])
+
+
 def qwen3_like(z):
     """Qwen3 at the same width, depth, head count and feed-forward parameter count (3 matrices instead of 2), with
     full attention (its cache of a 2,048-token context is read whole; Gigopel reads its window)."""
@@ -320,12 +354,34 @@ def compare_run(a):
         per_seq = half * (min(t, win) * 2 * G * (128 + 64) * 2 + 2 * R * 128 * 128 * 4)
         return flops, wbytes, per_seq
 
+    def fel_numbers(z, t):
+        """The same figures for a Felolorn model whose layers cycle through HGRN2, latent attention and lightning."""
+        W, H, d, dv, R, Q, S = z["width"], z["heads"], z["dim"], z["vdim"], z["kv_rank"], z["q_rank"], z["state_heads"]
+        n = [len(range(k, z["layers"], 3)) for k in range(3)]
+        hg = 3 * S * 128 * W + W * S * 128                     # q, f, v and the output matrix
+        la = (Q + R) * W + H * d * Q + H * (d + dv) * R + W * H * dv
+        li = 4 * S * 128 * W + W * S * 128                     # q, k, v, g and the output matrix
+        gates = 2 * W * W
+        ff_active = z["top"] * 3 * W * z["expert_ff"] + z["experts"] * W
+        ff_read = z["experts"] * 3 * W * z["expert_ff"] + z["experts"] * W
+        keys = t * (t + 1) // 2
+        mix = n[0] * hg + n[1] * la + n[2] * li
+        attn = n[1] * 2 * H * (d + dv) * keys + (n[0] + n[2]) * t * S * 2 * 2 * 128 * 128
+        flops = 2 * t * (mix + z["layers"] * (gates + ff_active)) + attn + 2 * z["vocab"] * W
+        wbytes = (mix + z["layers"] * (gates + ff_read)) * 2 + z["vocab"] * W * 2
+        per_seq = n[1] * t * R * 2 + (n[0] + n[2]) * 2 * S * 128 * 128 * 4
+        return flops, wbytes, per_seq
+
     out = {}
     T = PROMPT_LEN
     design = a.compare
     for name in [x for x in a.compare_sizes.split(",") if x.strip()]:
         z = GIGOPEL_SIZES[name]
-        if design == "sokirax":
+        if design == "felolorn":
+            zs, zf = SOKIRAX_SIZES[name], FELOLORN_SIZES[name]
+            arms = [("felolorn_experts", felolorn_config(zf)), ("sokirax_experts", sokirax_config(zs, "moe")),
+                    ("qwen3_like", qwen3_like(z))]
+        elif design == "sokirax":
             zs = SOKIRAX_SIZES[name]
             arms = [("sokirax_dense", sokirax_config(zs, "dense")), ("sokirax_experts", sokirax_config(zs, "moe")),
                     ("qwen3_like", qwen3_like(z))]
@@ -340,7 +396,9 @@ def compare_run(a):
             per_seq = 0
             if arm == "qwen3_like":
                 flops, wbytes = qwen_numbers(cd, z, T)
-            elif design == "sokirax":
+            elif arm == "felolorn_experts":
+                flops, wbytes, per_seq = fel_numbers(zf, T)
+            elif design in ("sokirax", "felolorn"):
                 flops, wbytes, per_seq = sok_numbers(zs, "dense" if arm.endswith("dense") else "moe", T)
             else:
                 flops, wbytes = gig_numbers(z, "dense" if arm.endswith("dense") else "moe", T)
@@ -353,12 +411,12 @@ def compare_run(a):
                 dms, kernels = decode_ms(model, b, T, max(16, min(a.steps, 64)), max(a.warmup, 3))
                 # experts: a step reads at most batch * top experts' matrices, not all of them
                 rb = wbytes
-                if arm in ("gigopel_experts", "sokirax_experts"):
+                if arm in ("gigopel_experts", "sokirax_experts", "felolorn_experts"):
                     used = min(z["experts"], b * z["top"])
                     rb -= z["layers"] * (z["experts"] - used) * 3 * z["width"] * z["expert_ff"] * 2
                 if arm == "qwen3_like":
                     rb += b * T * 2 * z["layers"] * 8 * 128 * 2
-                elif design == "sokirax":
+                elif design in ("sokirax", "felolorn"):
                     rb += b * per_seq
                 else:
                     rb += b * min(T, z["window"]) * z["layers"] * (z["kv_rank"] + z["rot_dim"]) * 2
@@ -397,7 +455,7 @@ def main():
                     "decode_by_context)")
     ap.add_argument("--prefill-lengths", default="", help="comma separated prompt lengths: time one prefill step of each "
                     "(printed on stderr, added to the line as prefill_sweep)")
-    ap.add_argument("--compare", default="", choices=["", "gigopel", "sokirax"],
+    ap.add_argument("--compare", default="", choices=["", "gigopel", "sokirax", "felolorn"],
                     help="another workload: the named design beside Qwen3 at equal size (prefill and decode), see the top")
     ap.add_argument("--compare-sizes", default="2k,4k", help="which of the comparison's layer sizes to run")
     a = ap.parse_args()

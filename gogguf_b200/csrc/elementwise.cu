@@ -778,10 +778,10 @@ GG_API gg_feed_tokens(int* tokens, const int* src, const int* sampled, int n, cu
 }
 
 // ----------------------------------------------------------------------------- short causal convolution over time
-// out[t, c] = h[t, c] * keep + sum_j w[c, j] * h[t - taps + 1 + j, c] (j < taps; the last tap meets the token
+// out[t, c] = h[t, c] * keep + sum_j w[j, c] * h[t - taps + 1 + j, c] (j < taps; the last tap meets the token
 // itself), per channel, inside each sequence; keep = 1 adds the convolution to its input.  Rows before the step's
 // first token come from the sequence's state [slot][taps - 1][W] (float32: the last taps - 1 input rows of the
-// sequence in order, zeros at its start).  One block per token.  The state is not written here: other blocks of
+// sequence in order, zeros at its start).  Blocks (token, 256 channels).  The state is not written here: other blocks of
 // the same sequence still read it (short_conv_state_kernel moves it on afterwards).
 template <typename T>
 __global__ void __launch_bounds__(256) short_conv_kernel(const T* h, T* out, const float* __restrict__ w,
@@ -794,26 +794,26 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const T* h, T* out, con
     const int b = seq_of_token[t];
     T* o = out + (size_t)t * W;
     if (b < 0) {
-        for (int c = threadIdx.x; c < W; c += blockDim.x) o[c] = from_f<T>(0.f);
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) o[c] = from_f<T>(0.f);
         return;
     }
     const int start = cu_seqlens[b];
     const int R = taps - 1;
     const float* st = state + (size_t)slots[b] * R * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float* wc = w + (size_t)c * taps;
-        float acc = to_f<T>(h[(size_t)t * W + c]) * (keep + wc[R]);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
+        const float* wc = w + c;                       // tap j of channel c at wc[j * W]
+        float acc = to_f<T>(h[(size_t)t * W + c]) * (keep + wc[(size_t)R * W]);
         for (int j = 0; j < R; ++j) {
             const int s = t - R + j;
             const float v = s >= start ? to_f<T>(h[(size_t)s * W + c]) : st[(size_t)(R + (s - start)) * W + c];
-            acc = fmaf(wc[j], v, acc);
+            acc = fmaf(wc[(size_t)j * W], v, acc);
         }
         o[c] = from_f<T>(acc);
     }
 }
 
 // The state after the step: the last taps - 1 input rows of every sequence (rows of the step where it brought
-// that many, else the old state moved up).  One block per sequence; a thread reads all it needs of a channel
+// that many, else the old state moved up).  Blocks (sequence, 256 channels); a thread reads all it needs of a channel
 // before it writes.  Padding sequences (seq_of_token < 0 at their first row) are left alone.
 #define CONV_MAX_TAPS 16
 template <typename T>
@@ -827,7 +827,7 @@ __global__ void __launch_bounds__(256) short_conv_state_kernel(const T* h, float
     if (n <= 0 || seq_of_token[start] < 0) return;
     const int R = taps - 1;
     float* st = state + (size_t)slots[b] * R * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
         float keep[CONV_MAX_TAPS];
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS; ++j) {
@@ -842,17 +842,151 @@ __global__ void __launch_bounds__(256) short_conv_state_kernel(const T* h, float
     }
 }
 
-// h and out [T, W] in `dtype` (they may not overlap), w [W][taps] float32, state [slots][taps - 1][W] float32.
+// The 16-byte form: a thread makes V = 16 / sizeof(T) neighbouring channels of one token (W a multiple of V) with
+// the tap count known at compile time; its loads of earlier rows meet other threads' in L1 and L2.  one_each != 0:
+// no sequence brings more than one token, so the thread that makes a token's channels is the only one that reads
+// its sequence's state there, and it moves the state on itself (no second launch).
+template <typename T> struct ConvRow;
+template <> struct ConvRow<float> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct ConvRow<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float* v) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h2[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float* v) {
+        uint4 a;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = a;
+    }
+};
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(256) short_conv_vec_kernel(const T* h, T* out, const float* __restrict__ w, float* state,
+                                                             const int* __restrict__ cu_seqlens,
+                                                             const int* __restrict__ slots,
+                                                             const int* __restrict__ seq_of_token, int W, int ntok,
+                                                             float keep, int one_each) {
+    pdl_launch();
+    pdl_wait();
+    constexpr int V = 16 / (int)sizeof(T);
+    constexpr int R = TAPS - 1;
+    const int per_row = W / V;
+    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (long long)ntok * per_row) return;
+    int t, c0;
+    if ((long long)ntok * per_row < (1ll << 31)) {
+        t = (int)((unsigned)item / (unsigned)per_row);
+        c0 = (int)((unsigned)item % (unsigned)per_row) * V;
+    } else {
+        t = (int)(item / per_row);
+        c0 = (int)(item % per_row) * V;
+    }
+    const int b = seq_of_token[t];
+    T* o = out + (size_t)t * W + c0;
+    float acc[V], x[V];
+    if (b < 0) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = 0.f;
+        ConvRow<T>::store(o, acc);
+        return;
+    }
+    float wr[TAPS * V];                                   // tap j of channel c0 + v at [j * V + v]
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+#pragma unroll
+        for (int v = 0; v < V; v += 4) ConvRow<float>::load(w + (size_t)j * W + c0 + v, wr + j * V + v);
+    }
+    ConvRow<T>::load(h + (size_t)t * W + c0, x);
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = x[v] * (keep + wr[R * V + v]);
+    if (R > 0) {
+        const int start = cu_seqlens[b];
+        float* st = state + (size_t)slots[b] * R * W + c0;
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const int s = t - R + j;
+            float prev[V];
+            if (s >= start) {
+                ConvRow<T>::load(h + (size_t)s * W + c0, prev);
+            } else {
+                const float* sr = st + (size_t)(R + (s - start)) * W;
+#pragma unroll
+                for (int v = 0; v < V; v += 4) ConvRow<float>::load(sr + v, prev + v);
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[v] = fmaf(wr[j * V + v], prev[v], acc[v]);
+            // one token of this sequence: row j of the old state was just read (s - start = j - R); it is row j - 1
+            // of the new one, which this thread read in the round before
+            if (one_each && j >= 1) {
+#pragma unroll
+                for (int v = 0; v < V; v += 4) ConvRow<float>::store(st + (size_t)(j - 1) * W + v, prev + v);
+            }
+        }
+        if (one_each) {
+#pragma unroll
+            for (int v = 0; v < V; v += 4) ConvRow<float>::store(st + (size_t)(R - 1) * W + v, x + v);
+        }
+    }
+    ConvRow<T>::store(o, acc);
+}
+
+template <typename T, int TAPS>
+static int short_conv_vec_launch(const T* h, T* out, const float* w, float* state, const int* cu_seqlens, const int* slots,
+                                 const int* seq_of_token, int ntok, int W, float keep, int one_each, cudaStream_t stream) {
+    const long long items = (long long)ntok * (W / (16 / (int)sizeof(T)));
+    return gg_launch(short_conv_vec_kernel<T, TAPS>, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, stream, 1, h, out,
+                     w, state, cu_seqlens, slots, seq_of_token, W, ntok, keep, one_each);
+}
+
+#define CONV_VEC_MAX_TAPS 8
+template <typename T>
+static int short_conv_vec(int taps, const T* h, T* out, const float* w, float* state, const int* cu_seqlens,
+                          const int* slots, const int* seq_of_token, int ntok, int W, float keep, int one_each,
+                          cudaStream_t stream) {
+#define CONV_CASE(N) case N: return short_conv_vec_launch<T, N>(h, out, w, state, cu_seqlens, slots, seq_of_token, ntok, W, \
+                                                                keep, one_each, stream);
+    switch (taps) { CONV_CASE(1) CONV_CASE(2) CONV_CASE(3) CONV_CASE(4) CONV_CASE(5) CONV_CASE(6) CONV_CASE(7) CONV_CASE(8) }
+#undef CONV_CASE
+    return GG_ERR_ARG;
+}
+
+// h and out [T, W] in `dtype` (they may not overlap), w [taps][W] float32 (a tap's weights side by side), state [slots][taps - 1][W] float32.
+// max_new: the most tokens one sequence brings (0: not known).
 GG_API gg_short_conv(const void* h, void* out, int dtype, const float* w, float* state, const int* cu_seqlens,
                      const int* slots, const int* seq_of_token, int ntok, int n_seqs, int W, int taps, float keep,
-                     cudaStream_t stream) {
+                     int max_new, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (W <= 0 || taps < 1 || taps > CONV_MAX_TAPS || (taps > 1 && state == nullptr)) return GG_ERR_ARG;
+    const int cb = min((W + 255) / 256, 65535);
+    const int one_each = max_new == 1;
     GG_DISPATCH_DTYPE(dtype, T,
-        gg_launch(short_conv_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, (const T*)h, (T*)out, w, (const float*)state,
-                  cu_seqlens, slots, seq_of_token, W, taps, keep);
-        if (taps > 1)
-            gg_launch(short_conv_state_kernel<T>, dim3(n_seqs), dim3(256), 0, stream, 1, (const T*)h, state, cu_seqlens,
+        const bool vec = taps <= CONV_VEC_MAX_TAPS && W % (16 / (int)sizeof(T)) == 0 && ((uintptr_t)h | (uintptr_t)out | (uintptr_t)w |
+                                                                          (uintptr_t)state) % 16 == 0;
+        if (vec) {
+            short_conv_vec<T>(taps, (const T*)h, (T*)out, w, state, cu_seqlens, slots, seq_of_token, ntok, W, keep, one_each,
+                              stream);
+        } else {
+            // a thread per channel: blocks of 256 channels side by side
+            gg_launch(short_conv_kernel<T>, dim3(ntok, cb), dim3(256), 0, stream, 1, (const T*)h, (T*)out, w,
+                      (const float*)state, cu_seqlens, slots, seq_of_token, W, taps, keep);
+        }
+        if (taps > 1 && !(vec && one_each))
+            gg_launch(short_conv_state_kernel<T>, dim3(n_seqs, cb), dim3(256), 0, stream, 1, (const T*)h, state, cu_seqlens,
                       slots, seq_of_token, W, taps));
     return gg_last_error();
 }

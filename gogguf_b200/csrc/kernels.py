@@ -167,10 +167,14 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
 
 def short_conv(h: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor],
                cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor, n_tokens: int, n_seqs: int,
-               keep: float = 1.0) -> None:
-    """out[t] = keep * h[t] + sum_j weight[:, j] * h[t - taps + 1 + j] per channel inside each sequence; rows before
-    the step come from state [slots, taps - 1, W] (float32), which is then moved on to the step's last rows."""
-    W, taps = weight.shape
+               keep: float = 1.0, max_new: int = 0) -> None:
+    """out[t] = keep * h[t] + sum_j weight[j] * h[t - taps + 1 + j] per channel inside each sequence (weight is
+    [taps, W]: a tap's weights side by side, the last tap meets the token itself); rows before
+    the step come from state [slots, taps - 1, W] (float32), which is then moved on to the step's last rows.
+    max_new: the most tokens one sequence brings, where the caller knows it (1: a single launch does both)."""
+    taps, W = weight.shape
+    if not weight.is_contiguous():
+        raise KernelError("short_conv: the taps are a contiguous [taps, W]")
     if h.dtype != out.dtype or not h.is_contiguous() or not out.is_contiguous() or h.shape[-1] != W:
         raise KernelError("short_conv: h and out are contiguous [T, W] of one dtype")
     if h.data_ptr() == out.data_ptr():
@@ -182,7 +186,7 @@ def short_conv(h: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: 
             raise KernelError("short_conv: the state is [slots, taps - 1, W]")
     kernel("elementwise", "gg_short_conv")(_p(h), _p(out), dtype_code(h.dtype), _p(weight), _p(state), _p(cu_seqlens),
                                             _p(slots), _p(seq_of_token), int(n_tokens), int(n_seqs), W, taps, float(keep),
-                                            _stream())
+                                            int(max_new), _stream())
 
 
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows: int) -> None:
@@ -414,6 +418,43 @@ def gated_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, raw: torch.T
         _p(x), dtype_code(x.dtype), x.stride(0), int(q_off), int(k_off), int(v_off), _p(raw), _p(state), _p(cu_seqlens),
         _p(slots), _p(seq_of_token), _p(decay), _p(forget_bias), _p(forget_lower), gate, int(n_tokens), int(n_seqs),
         int(heads), int(d), int(dv), int(act_q), int(act_k), int(act_v), _stream())
+
+
+SCAN_CHUNK = 64               # tokens per chunk of the many-CTA form (REC_PC in csrc/recurrence.cu)
+SCAN_CHUNKS_MAX_HEAD = 128
+
+
+def gated_scan_chunks_scratch(n_tokens: int, n_seqs: int, heads: int, d: int, dv: int) -> int:
+    """Floats of scratch `gated_scan_chunks` needs: a state and a decay per chunk and head."""
+    return (n_tokens // SCAN_CHUNK + n_seqs) * heads * d * (dv + 1)
+
+
+def gated_scan_chunks(x: torch.Tensor, q_off: int, k_off: int, v_off: int, raw: torch.Tensor, scratch: torch.Tensor,
+                      state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor,
+                      n_tokens: int, n_seqs: int, heads: int, d: int, dv: int, decay: Optional[torch.Tensor] = None,
+                      forget_bias: Optional[torch.Tensor] = None, forget_lower: Optional[torch.Tensor] = None,
+                      act_q: int = 0, act_k: int = 0, act_v: int = 0) -> None:
+    """`gated_scan` for prompts, cut so that every chunk of 64 tokens of every head is a CTA of its own: what each
+    chunk adds to the state, a walk over the chunks' states, the outputs chunk by chunk (head sizes up to 128)."""
+    if x.stride(-1) != 1:
+        raise KernelError("gated_scan: rows of x must be contiguous")
+    _need(raw, torch.float32, "raw")
+    _need(state, torch.float32, "state")
+    _need(scratch, torch.float32, "scratch")
+    if tuple(state.shape[1:]) != (heads, d, dv) or raw.shape[-1] != heads * dv:
+        raise KernelError("gated_scan: the state must be [slots, heads, d, dv] and raw [T, heads * dv]")
+    if scratch.numel() < gated_scan_chunks_scratch(n_tokens, n_seqs, heads, d, dv):
+        raise KernelError("gated_scan: the scratch is too small")
+    gate = 0 if decay is not None else 1
+    for t, n in ((decay, heads), (forget_bias, heads * d), (forget_lower, heads * d)):
+        if t is not None:
+            _need(t, torch.float32, "recurrence constants")
+            if t.numel() != n:
+                raise KernelError("gated_scan: decay is [heads], the forget gate's bias and lower bound [heads * d]")
+    kernel("recurrence", "gg_gated_scan_chunks")(
+        _p(x), dtype_code(x.dtype), x.stride(0), int(q_off), int(k_off), int(v_off), _p(raw), _p(scratch), _p(state),
+        _p(cu_seqlens), _p(slots), _p(seq_of_token), _p(decay), _p(forget_bias), _p(forget_lower), gate, int(n_tokens),
+        int(n_seqs), int(heads), int(d), int(dv), int(act_q), int(act_k), int(act_v), _stream())
 
 
 def scan_finish(raw: torch.Tensor, x: Optional[torch.Tensor], g_off: int, out: torch.Tensor,

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample|latent|retention] [--m 1,8,64] [--ctx 2048,8192]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample|latent|retention|recurrence] [--m 1,8,64] [--ctx 2048,8192]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -325,9 +325,96 @@ def retention(sizes=((8, 128, 128, 2048), (16, 128, 128, 4096))) -> None:
         torch.cuda.empty_cache()
 
 
+def recurrence(sizes=((8, 128, 128, 2048), (16, 128, 128, 4096))) -> None:
+    """The matrix-state scan (csrc/recurrence.cu) at layer sizes (heads, d, dv, width), with a fixed decay and with
+    a forget gate per channel: a prompt of 2,048 tokens against the float32 multiply-add rate of the CUDA cores
+    (the state and all that enters it are 32-bit), decode steps against the copy bandwidth (a step reads and
+    writes every state), then the finish kernel, the short convolution and the gated norm-and-add."""
+    from . import kernels as K
+    dev = "cuda:0"
+    hbm, _, src = _peaks()
+    props = torch.cuda.get_device_properties(0)
+    fp32_tflops = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
+    print(f"peaks ({src}): {hbm:.0f} GB/s copy; float32 multiply-add rate {fp32_tflops:.1f} TFLOP/s (nominal, 1,965 MHz)")
+    for H, d, dv, W in sizes:
+        width = 2 * H * d + 2 * H * dv
+        decay = torch.linspace(0.97, 0.9995, H, device=dev)
+        fb, fl = torch.zeros(H * d, device=dev), torch.full((H * d,), 0.9, device=dev)
+        T = 2048
+        nbuf = 4
+        xs = [(torch.randn(T, width, device=dev) * 0.5).to(torch.bfloat16) for _ in range(nbuf)]
+        raw = torch.empty(T, H * dv, device=dev)
+        out = torch.empty(T, H * dv, device=dev, dtype=torch.bfloat16)
+        state = torch.zeros(1, H, d, dv, device=dev)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        zero = torch.zeros(1, dtype=torch.int32, device=dev)
+        sot = torch.zeros(T, dtype=torch.int32, device=dev)
+        wn = torch.ones(H * dv, device=dev)
+        for name, kw in (("fixed decay", dict(decay=decay, act_k=1, act_v=1)), ("forget gate", dict(forget_bias=fb, forget_lower=fl))):
+            us = _time_graph(lambda i: K.gated_scan(xs[i % nbuf], 0, H * d, 2 * H * d, raw, state, cu, zero, sot, T, 1, H, d, dv,
+                                                    act_q=1, **kw), reps=10)
+            flops = 2 * T * H * 2 * d * dv
+            print(f"scan prompt  {name} H={H} d={d} dv={dv} T={T}: {us:8.1f} us  {flops / us / 1e6:6.2f} TFLOP/s "
+                  f"({flops / us / 1e6 / fp32_tflops:.2f} of the float32 rate)", flush=True)
+            scratch = torch.empty(K.gated_scan_chunks_scratch(T, 1, H, d, dv), device=dev)
+            us = _time_graph(lambda i: K.gated_scan_chunks(xs[i % nbuf], 0, H * d, 2 * H * d, raw, scratch, state, cu, zero, sot,
+                                                           T, 1, H, d, dv, act_q=1, **kw), reps=10)
+            # per chunk of 64 and head: the chunk's addition to the state, the products of q and k rows (half of
+            # them below the diagonal), their product with v, the incoming state's share of the outputs
+            cflops = 2 * T * H * (2 * d * dv + 32 * d + 32 * dv)
+            print(f"chunked      {name} H={H} d={d} dv={dv} T={T}: {us:8.1f} us  {cflops / us / 1e6:6.2f} TFLOP/s "
+                  f"({cflops / us / 1e6 / fp32_tflops:.2f} of the float32 rate; three launches)", flush=True)
+            for B in (8, 64):
+                slots = 512 // B * B
+                st = torch.zeros(slots, H, d, dv, device=dev)       # 512 states: beyond L2 in turns
+                x1 = (torch.randn(B, width, device=dev) * 0.5).to(torch.bfloat16)
+                r1 = torch.empty(B, H * dv, device=dev)
+                cu1 = torch.arange(B + 1, dtype=torch.int32, device=dev)
+                sot1 = torch.arange(B, dtype=torch.int32, device=dev)
+                sl = [torch.arange(k * B, (k + 1) * B, dtype=torch.int32, device=dev) for k in range(slots // B)]
+                us = _time_graph(lambda i: K.gated_scan(x1, 0, H * d, 2 * H * d, r1, st, cu1, sl[i % len(sl)], sot1, B, B, H, d, dv,
+                                                        act_q=1, **kw))
+                nbytes = 2 * B * H * d * dv * 4
+                print(f"scan decode  {name} H={H} d={d} dv={dv} batch {B:3d}: {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
+                      f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)
+        for rows in (8, 64, 2048):
+            x = xs[0][:rows]
+            us = _time_graph(lambda i: K.scan_finish(raw[:rows], x, 2 * H * d + H * dv, out[:rows], wn, sot[:rows], rows, H, dv, 1e-6,
+                                                     whole=True, gate=1))
+            nbytes = rows * H * dv * (4 + 2 + 2)
+            print(f"scan finish       heads {H} x {dv} rows {rows:4d}: {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
+                  f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)
+        taps = 4
+        cw = torch.randn(taps, W, device=dev) * 0.1
+        for rows in (8, 64, 2048):
+            n = max(2, int(300e6 // (rows * W * 4)) + 1) if rows >= 2048 else 2
+            hs = [torch.randn(rows, W, device=dev).to(torch.bfloat16) for _ in range(n)]
+            ho = torch.empty(rows, W, device=dev, dtype=torch.bfloat16)
+            B = rows if rows < 2048 else 1
+            cst = torch.zeros(B, taps - 1, W, device=dev)
+            cuB = torch.arange(B + 1, dtype=torch.int32, device=dev) * (rows // B)
+            sotB = torch.arange(rows, dtype=torch.int32, device=dev) // (rows // B)
+            slB = torch.arange(B, dtype=torch.int32, device=dev)
+            us = _time_graph(lambda i: K.short_conv(hs[i % n], ho, cw, cst, cuB, slB, sotB, rows, B, max_new=rows // B))
+            nbytes = rows * W * (2 + 2)
+            print(f"short conv        width {W} taps {taps} rows {rows:4d}: {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
+                  f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth; {'one launch' if rows == B else 'two launches'})", flush=True)
+            n = max(2, int(300e6 // (rows * W * 12)) + 1) if rows >= 2048 else 2
+            x = [torch.randn(rows, W, device=dev) for _ in range(n)]
+            y = [torch.randn(rows, W, device=dev) for _ in range(n)]
+            gt = [torch.randn(rows, W, device=dev) for _ in range(n)]
+            w = torch.ones(W, device=dev)
+            us = _time_graph(lambda i: K.rmsnorm_add(x[i % n], y[i % n], w, 1e-6, zero_y=True, gate=gt[i % n], gate_bias=w))
+            nbytes = rows * W * (4 + 4 + 4 + 4 + 4)
+            print(f"gated norm-and-add width {W} rows {rows:4d}: {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
+                  f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)
+        del xs
+        torch.cuda.empty_cache()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample", "latent", "retention"])
+    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample", "latent", "retention", "recurrence"])
     ap.add_argument("--m", default="1,8,64", help="token counts (gemm), batch sizes (attn) or prompt lengths (prefill_attn)")
     ap.add_argument("--ctx", default="2048", help="attn: cached positions per sequence (comma separated)")
     ap.add_argument("--scratch", action="store_true", help="attn: splits merged by a second kernel instead of inside clusters")
@@ -338,6 +425,9 @@ def main() -> None:
         return
     if a.what == "retention":
         retention()
+        return
+    if a.what == "recurrence":
+        recurrence()
         return
     if a.what == "attn":
         for c in a.ctx.split(","):

@@ -209,3 +209,339 @@ GG_API gg_scan_finish(const float* raw, const void* x, int dtype, long long ld, 
                   seq_of_token, H, dv, eps, out_scale, whole, gate));
     return gg_last_error();
 }
+
+// ----------------------------------------------------------------------------- prompts over many CTAs
+// The same sums cut into chunks of REC_PC tokens, every (chunk, head) a CTA of its own, in three kernels.  With
+// i, j counting a chunk's n tokens from 0 and G_i = g_0 g_1 ... g_i (per channel r, the row of the state):
+//   1. what the chunk adds to the state:   U = sum_j diag(G_(n-1) / G_j) k_j v_j^T,   D = G_(n-1)
+//   2. a walk over a sequence's chunks:    S_in(c + 1) = diag(D_c) S_in(c) + U_c, from the slot's state and into it
+//   3. the outputs:   o_i = S_in^T (G_i * q_i) + sum_{j <= i} A_ij v_j,   A_ij = sum_r q_i[r] k_j[r] G_i[r] / G_j[r]
+// A fixed decay makes every ratio a power of one number, so A is a product of q and k rows times decay^(i - j).
+// With a forget gate per channel the ratios are formed as 2^(L_i[r] - L_j[r]) from running sums L of log2 g (each
+// log2 held above REC_LOG2_FLOOR, far below what float32 tells from zero): never a quotient of two small numbers,
+// and no ratio above one.  float32 on the CUDA cores; 16 x 16 threads with register tiles; d, dv <= REC_PMAX.
+// The running sums lose about |L| ulps against the token-by-token form, which is rounding next to 16-bit
+// projections; the 32-bit path keeps the scan above.
+#define REC_PC 64
+#define REC_PMAX 128
+#define REC_LOG2_FLOOR -150.0f
+
+// Which (sequence, chunk) is CTA `item`?  Chunks are numbered sequence after sequence, padding rows have none.
+__device__ __forceinline__ bool rec_find_chunk(int item, const int* cu_seqlens, const int* seq_of_token, int n_seqs,
+                                               int& b, int& t0, int& n) {
+    for (int i = 0; i < n_seqs; ++i) {
+        const int a = cu_seqlens[i], e = cu_seqlens[i + 1];
+        if (e <= a || seq_of_token[a] < 0) continue;
+        const int nc = (e - a + REC_PC - 1) / REC_PC;
+        if (item < nc) { b = i; t0 = a + item * REC_PC; n = min(REC_PC, e - t0); return true; }
+        item -= nc;
+    }
+    return false;
+}
+
+// q (if qs), k and, with a forget gate, log2 g (if ls) of head h for n tokens from row t0, float32, into shared
+// memory.  q rows are qstride apart; k and log2 g rows kstride apart, element i of row tt in column
+// i ^ (tt & 31) when swz (unpadded rows whose columns are then read from different banks by different rows).
+template <typename T, bool GATED>
+__device__ __forceinline__ void rec_stage_qk(const T* x, long long ld, int q_off, int k_off, int t0, int n, int h, int d,
+                                             const float* __restrict__ fbias, const float* __restrict__ flow, int act_q,
+                                             int act_k, float* qs, int qstride, float* ks, float* ls, int kstride, bool swz) {
+    for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {
+        const int tt = idx / d, i = idx - tt * d;
+        const T* row = x + (size_t)(t0 + tt) * ld;
+        if (qs) qs[tt * qstride + i] = rec_act(to_f<T>(row[q_off + h * d + i]), act_q);
+        const float kz = to_f<T>(row[k_off + h * d + i]);
+        const int at = tt * kstride + (swz ? (i ^ (tt & 31)) : i);
+        if (GATED) {
+            const float lo = flow[h * d + i];
+            const float f = lo + (1.0f - lo) * rec_sigmoid(kz + fbias[h * d + i]);
+            ks[at] = 1.0f - f;
+            if (ls) ls[at] = fmaxf(log2f(f), REC_LOG2_FLOOR);
+        } else {
+            ks[at] = rec_act(kz, act_k);
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void rec_stage_v(const T* x, long long ld, int v_off, int t0, int n, int h, int dv, int act_v,
+                                            float* vs) {
+    for (int idx = threadIdx.x; idx < n * dv; idx += blockDim.x) {
+        const int tt = idx / dv, j = idx - tt * dv;
+        vs[tt * dv + j] = rec_act(to_f<T>(x[(size_t)(t0 + tt) * ld + v_off + h * dv + j]), act_v);
+    }
+}
+
+// 1. U [chunk][H][d][dv] and D [chunk][H][d].
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256) rec_chunk_state_kernel(
+    const T* x, long long ld, int q_off, int k_off, int v_off, float* U, float* D, const int* __restrict__ cu_seqlens,
+    const int* __restrict__ seq_of_token, const float* __restrict__ decay, const float* __restrict__ fbias,
+    const float* __restrict__ flow, int n_seqs, int H, int d, int dv, int act_k, int act_v) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float sm[];
+    int b, t0, n;
+    if (!rec_find_chunk(blockIdx.x, cu_seqlens, seq_of_token, n_seqs, b, t0, n)) return;
+    const int h = blockIdx.y, ds = d + 1;
+    float* ks = sm;                        // [PC][ds], in the end times G_(n-1) / G_j
+    float* vs = ks + REC_PC * ds;          // [PC][dv]
+    float* ls = vs + REC_PC * dv;          // [PC][ds] (GATED only)
+    rec_stage_qk<T, GATED>(x, ld, q_off, k_off, t0, n, h, d, fbias, flow, 0, act_k, nullptr, 0, ks, GATED ? ls : nullptr,
+                           ds, false);
+    rec_stage_v<T>(x, ld, v_off, t0, n, h, dv, act_v, vs);
+    __syncthreads();
+    for (int r = threadIdx.x; r < d; r += blockDim.x) {      // a thread owns channel r of every token
+        float* dp = D + ((size_t)blockIdx.x * H + h) * d;
+        if (GATED) {
+            float run = 0.f;
+            for (int tt = 0; tt < n; ++tt) { run += ls[tt * ds + r]; ls[tt * ds + r] = run; }
+            for (int tt = 0; tt < n; ++tt) ks[tt * ds + r] *= exp2f(run - ls[tt * ds + r]);
+            dp[r] = exp2f(run);
+        } else {
+            const float a = decay[h];
+            float p = 1.f;
+            for (int tt = n - 1; tt >= 0; --tt) { ks[tt * ds + r] *= p; p *= a; }
+            dp[r] = p;
+        }
+    }
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[REC_PMAX / 16][REC_PMAX / 16];
+#pragma unroll
+    for (int i = 0; i < REC_PMAX / 16; ++i)
+#pragma unroll
+        for (int j = 0; j < REC_PMAX / 16; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+        float kr[REC_PMAX / 16], vc[REC_PMAX / 16];
+#pragma unroll
+        for (int i = 0; i < REC_PMAX / 16; ++i) {
+            kr[i] = ty + 16 * i < d ? ks[j * ds + ty + 16 * i] : 0.f;
+            vc[i] = tx + 16 * i < dv ? vs[j * dv + tx + 16 * i] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < REC_PMAX / 16; ++i)
+#pragma unroll
+            for (int c = 0; c < REC_PMAX / 16; ++c) acc[i][c] = fmaf(kr[i], vc[c], acc[i][c]);
+    }
+    float* up = U + ((size_t)blockIdx.x * H + h) * d * dv;
+#pragma unroll
+    for (int i = 0; i < REC_PMAX / 16; ++i)
+#pragma unroll
+        for (int c = 0; c < REC_PMAX / 16; ++c)
+            if (ty + 16 * i < d && tx + 16 * c < dv) up[(size_t)(ty + 16 * i) * dv + tx + 16 * c] = acc[i][c];
+}
+
+// 2. The walk: U[c] becomes the state chunk c starts from, the slot's state the one after the last chunk.
+__global__ void __launch_bounds__(256) rec_chunk_walk_kernel(
+    float* U, const float* D, float* state, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+    const int* __restrict__ seq_of_token, int H, int d, int dv) {
+    pdl_launch();
+    pdl_wait();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int start = cu_seqlens[b], end = cu_seqlens[b + 1];
+    if (e >= d * dv || end <= start || seq_of_token[start] < 0) return;
+    int base = 0;
+    for (int i = 0; i < b; ++i) {
+        const int a0 = cu_seqlens[i], e0 = cu_seqlens[i + 1];
+        if (e0 > a0 && seq_of_token[a0] >= 0) base += (e0 - a0 + REC_PC - 1) / REC_PC;
+    }
+    const int nch = (end - start + REC_PC - 1) / REC_PC;
+    float* sp = state + (((size_t)slots[b] * H + h) * d) * dv + e;
+    float s = *sp;
+    const size_t step = (size_t)H * d * dv, dstep = (size_t)H * d;
+    float* up = U + ((size_t)base * H + h) * d * dv + e;
+    const float* dp = D + ((size_t)base * H + h) * d + e / dv;
+    // eight chunks' terms are asked for at once: the walk itself is a chain of dependent multiply-adds only
+    for (int c0 = 0; c0 < nch; c0 += 8) {
+        float u[8], g[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            u[k] = c0 + k < nch ? up[(size_t)(c0 + k) * step] : 0.f;
+            g[k] = c0 + k < nch ? dp[(size_t)(c0 + k) * dstep] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (c0 + k < nch) {
+                up[(size_t)(c0 + k) * step] = s;
+                s = fmaf(s, g[k], u[k]);
+            }
+        }
+    }
+    *sp = s;
+}
+
+// 3. The outputs of a chunk from the state it starts with (Sin, what the walk left in U) and its own tokens.
+// Shared memory is cut so that two CTAs share an SM at 128 x 128 heads: q rows unpadded (read as broadcasts), k
+// (and log2 g) rows unpadded with swizzled columns where d is a multiple of 32 (else padded by one); with a
+// forget gate the v rows arrive in the place of the running sums once A is made.
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256, 2) rec_chunk_out_kernel(
+    const T* x, long long ld, int q_off, int k_off, int v_off, float* raw, const float* Sin,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token, const float* __restrict__ decay,
+    const float* __restrict__ fbias, const float* __restrict__ flow, int n_seqs, int H, int d, int dv, int act_q,
+    int act_k, int act_v) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float sm[];
+    int b, t0, n;
+    if (!rec_find_chunk(blockIdx.x, cu_seqlens, seq_of_token, n_seqs, b, t0, n)) return;
+    const bool swz = (d & 31) == 0;
+    const int h = blockIdx.y, ds = swz ? d : d + 1;
+    float* qs = sm;                                   // [PC][d]
+    float* ks = qs + REC_PC * d;                      // [PC][ds]
+    float* vs = ks + REC_PC * ds;                     // [PC][max(ds, dv)]: v rows; GATED: first the running sums
+    float* ls = vs;
+    float* A = vs + REC_PC * max(ds, dv);             // [PC][PC]
+    float* pw = A + REC_PC * REC_PC;                  // [PC + 1]: powers of the decay (not GATED)
+    if (!GATED && threadIdx.x <= REC_PC) {
+        const float a = decay[h];
+        float p = 1.f;
+        for (int i = 0; i < (int)threadIdx.x; ++i) p *= a;
+        pw[threadIdx.x] = p;
+    }
+    rec_stage_qk<T, GATED>(x, ld, q_off, k_off, t0, n, h, d, fbias, flow, act_q, act_k, qs, d, ks, GATED ? ls : nullptr, ds,
+                           swz);
+    if (!GATED) rec_stage_v<T>(x, ld, v_off, t0, n, h, dv, act_v, vs);
+    __syncthreads();
+    if (GATED) {
+        for (int r = threadIdx.x; r < d; r += blockDim.x) {
+            float run = 0.f;
+            for (int tt = 0; tt < n; ++tt) {
+                const int at = tt * ds + (swz ? (r ^ (tt & 31)) : r);
+                run += ls[at];
+                ls[at] = run;
+            }
+        }
+        __syncthreads();
+    }
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    {   // A[i][j] for j <= i < n, else 0; rows i = ty + 16 a, columns j = tx + 16 b; b > a lies above the diagonal
+        float acc[REC_PC / 16][REC_PC / 16];
+#pragma unroll
+        for (int i = 0; i < REC_PC / 16; ++i)
+#pragma unroll
+            for (int j = 0; j < REC_PC / 16; ++j) acc[i][j] = 0.f;
+#pragma unroll 2
+        for (int r = 0; r < d; ++r) {
+            float qv[REC_PC / 16], kv[REC_PC / 16], lq[REC_PC / 16], lk[REC_PC / 16];
+#pragma unroll
+            for (int i = 0; i < REC_PC / 16; ++i) {
+                const int qi = ty + 16 * i, kj = tx + 16 * i;
+                qv[i] = qi < n ? qs[qi * d + r] : 0.f;
+                kv[i] = kj < n ? ks[kj * ds + (swz ? (r ^ (kj & 31)) : r)] : 0.f;
+                if (GATED) {
+                    lq[i] = qi < n ? ls[qi * ds + (swz ? (r ^ (qi & 31)) : r)] : 0.f;
+                    lk[i] = kj < n ? ls[kj * ds + (swz ? (r ^ (kj & 31)) : r)] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < REC_PC / 16; ++i)
+#pragma unroll
+                for (int j = 0; j < REC_PC / 16; ++j) {
+                    if (GATED) {
+                        if (j <= i) acc[i][j] = fmaf(qv[i] * kv[j], exp2f(fminf(lq[i] - lk[j], 0.f)), acc[i][j]);
+                    } else {
+                        acc[i][j] = fmaf(qv[i], kv[j], acc[i][j]);
+                    }
+                }
+        }
+        __syncthreads();                          // every thread is done with the q rows and the running sums as they are
+#pragma unroll
+        for (int i = 0; i < REC_PC / 16; ++i)
+#pragma unroll
+            for (int j = 0; j < REC_PC / 16; ++j) {
+                const int qi = ty + 16 * i, kj = tx + 16 * j;
+                const float wgt = GATED ? 1.f : pw[max(qi - kj, 0)];
+                A[qi * REC_PC + kj] = (kj <= qi && qi < n) ? acc[i][j] * wgt : 0.f;
+            }
+    }
+    // q_i times G_i, in place
+    for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {
+        const int tt = idx / d, i = idx - tt * d;
+        qs[idx] *= GATED ? exp2f(ls[tt * ds + (swz ? (i ^ (tt & 31)) : i)]) : pw[tt + 1];
+    }
+    __syncthreads();
+    if (GATED) rec_stage_v<T>(x, ld, v_off, t0, n, h, dv, act_v, vs);
+    // o[i][c]: rows i = ty + 16 a, columns c = tx + 16 b
+    float o[REC_PC / 16][REC_PMAX / 16];
+#pragma unroll
+    for (int i = 0; i < REC_PC / 16; ++i)
+#pragma unroll
+        for (int c = 0; c < REC_PMAX / 16; ++c) o[i][c] = 0.f;
+    const float* S = Sin + ((size_t)blockIdx.x * H + h) * d * dv;
+#pragma unroll 4
+    for (int r = 0; r < d; ++r) {
+        float qv[REC_PC / 16], sv[REC_PMAX / 16];
+#pragma unroll
+        for (int i = 0; i < REC_PC / 16; ++i) qv[i] = ty + 16 * i < n ? qs[(ty + 16 * i) * d + r] : 0.f;
+#pragma unroll
+        for (int c = 0; c < REC_PMAX / 16; ++c) sv[c] = tx + 16 * c < dv ? S[(size_t)r * dv + tx + 16 * c] : 0.f;
+#pragma unroll
+        for (int i = 0; i < REC_PC / 16; ++i)
+#pragma unroll
+            for (int c = 0; c < REC_PMAX / 16; ++c) o[i][c] = fmaf(qv[i], sv[c], o[i][c]);
+    }
+    __syncthreads();                              // the v rows are whole (and so is A)
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+        float av[REC_PC / 16], vv[REC_PMAX / 16];
+#pragma unroll
+        for (int i = 0; i < REC_PC / 16; ++i) av[i] = A[(ty + 16 * i) * REC_PC + j];
+#pragma unroll
+        for (int c = 0; c < REC_PMAX / 16; ++c) vv[c] = tx + 16 * c < dv ? vs[j * dv + tx + 16 * c] : 0.f;
+#pragma unroll
+        for (int i = 0; i < REC_PC / 16; ++i)
+#pragma unroll
+            for (int c = 0; c < REC_PMAX / 16; ++c) o[i][c] = fmaf(av[i], vv[c], o[i][c]);
+    }
+    const size_t HV = (size_t)H * dv;
+#pragma unroll
+    for (int i = 0; i < REC_PC / 16; ++i)
+#pragma unroll
+        for (int c = 0; c < REC_PMAX / 16; ++c)
+            if (ty + 16 * i < n && tx + 16 * c < dv) raw[(size_t)(t0 + ty + 16 * i) * HV + h * dv + tx + 16 * c] = o[i][c];
+}
+
+static inline size_t rec_chunk_smem_state(int d, int dv, int gate) {
+    return ((size_t)REC_PC * ((gate ? 2 : 1) * (d + 1) + dv)) * sizeof(float);
+}
+static inline size_t rec_chunk_smem_out(int d, int dv) {
+    const int ds = (d & 31) == 0 ? d : d + 1;
+    return ((size_t)REC_PC * (d + ds + (ds > dv ? ds : dv) + REC_PC) + REC_PC + 1) * sizeof(float);
+}
+
+// The chunked form of gg_gated_scan for steps that bring prompts: the same arguments, and scratch of
+// (ntok / 64 + n_seqs) * H * d * (dv + 1) floats (a state and a decay per chunk and head).  d, dv <= 128.
+GG_API gg_gated_scan_chunks(const void* x, int dtype, long long ld, int q_off, int k_off, int v_off, float* raw,
+                            float* scratch, float* state, const int* cu_seqlens, const int* slots, const int* seq_of_token,
+                            const float* decay, const float* fbias, const float* flow, int gate, int ntok, int n_seqs, int H,
+                            int d, int dv, int act_q, int act_k, int act_v, cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (H <= 0 || H > 65535 || d <= 0 || dv <= 0 || d > REC_PMAX || dv > REC_PMAX || raw == nullptr || state == nullptr ||
+        scratch == nullptr) return GG_ERR_ARG;
+    if (gate == 0 ? decay == nullptr : (gate != 1 || fbias == nullptr || flow == nullptr)) return GG_ERR_ARG;
+    const int chunks = ntok / REC_PC + n_seqs;
+    float* U = scratch;
+    float* D = scratch + (size_t)chunks * H * d * dv;
+    const size_t smem_a = rec_chunk_smem_state(d, dv, gate), smem_c = rec_chunk_smem_out(d, dv);
+#define GG_CHUNKS(T_, G_)                                                                                              \
+    do {                                                                                                               \
+        if (smem_a > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(rec_chunk_state_kernel<T_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a); \
+        if (smem_c > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(rec_chunk_out_kernel<T_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);  \
+        gg_launch(rec_chunk_state_kernel<T_, G_>, dim3(chunks, H), dim3(256), smem_a, stream, 1, (const T_*)x, ld, q_off,  \
+                  k_off, v_off, U, D, cu_seqlens, seq_of_token, decay, fbias, flow, n_seqs, H, d, dv, act_k, act_v);       \
+        gg_launch(rec_chunk_walk_kernel, dim3(n_seqs, H, (d * dv + 255) / 256), dim3(256), 0, stream, 1, U,               \
+                  (const float*)D, state, cu_seqlens, slots, seq_of_token, H, d, dv);                                     \
+        gg_launch(rec_chunk_out_kernel<T_, G_>, dim3(chunks, H), dim3(256), smem_c, stream, 1, (const T_*)x, ld, q_off,    \
+                  k_off, v_off, raw, (const float*)U, cu_seqlens, seq_of_token, decay, fbias, flow, n_seqs, H, d, dv,     \
+                  act_q, act_k, act_v);                                                                                   \
+    } while (0)
+    GG_DISPATCH_DTYPE(dtype, T, if (gate) GG_CHUNKS(T, true); else GG_CHUNKS(T, false));
+#undef GG_CHUNKS
+    return gg_last_error();
+}

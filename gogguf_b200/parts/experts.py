@@ -91,7 +91,8 @@ class RoutedExperts:
         n = cls._names(spec)
         t = {n["router"]: TensorDecl(shape=(E, h))}
         if spec.get("correction"):
-            t[n["correction"]] = TensorDecl(shape=(E,), init="small_normal")
+            # (a correction evens out the experts' load: small next to the scores' spread, or the choice is its alone)
+            t[n["correction"]] = TensorDecl(shape=(E,), init="zeros_normal")
         for e in range(E):
             p = n["expert"].format(e)
             t[p + n["gate"]] = TensorDecl(shape=(i, h))

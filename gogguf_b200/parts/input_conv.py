@@ -56,7 +56,8 @@ class InputConvMixer:
         if self.taps < 1:
             raise ValueError("input_conv: taps must be at least 1")
         self.keep = 1.0 if spec.get("residual", True) else 0.0
-        self.weight = rt.vector(weights[spec.get("tensor", "conv.weight")])      # float32 [W, taps]
+        # stored [W, taps]; kept as float32 [taps, W], a tap's weights side by side
+        self.weight = rt.vector(weights[spec.get("tensor", "conv.weight")]).t().contiguous()
         ps, mcls = _inner(spec)
         own = {local: weights[ps.prefix + local] for local in mcls.tensors(ps) if ps.prefix + local in weights}
         self.inner = mcls(ps, own, rt)
@@ -81,5 +82,5 @@ class InputConvMixer:
         tail, view = cache
         fed = ctx.ws.get("input_conv_out", tuple(h.shape), h.dtype)
         K.short_conv(h, fed, self.weight, tail.state if tail is not None else None, ctx.cu_seqlens, ctx.slots,
-                     ctx.seq_of_token, ctx.n_tokens, ctx.n_seqs, self.keep)
+                     ctx.seq_of_token, ctx.n_tokens, ctx.n_seqs, self.keep, max_new=int(ctx.max_new))
         self.inner.forward(fed, residual, ctx, view, writes_cache)

@@ -23,6 +23,7 @@ head).  The activations, the norm's extent and the output gate are parameters to
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List
 
 import torch
@@ -33,6 +34,8 @@ from ..csrc import kernels as K
 from ..weights.loader import TensorDecl
 from .base import Linear, Runtime, StepContext
 from .registry import register_mixer
+
+CHUNKED_FROM = 64       # new tokens of one sequence from which a step takes the chunked form
 
 _ACT = {"none": 0, "silu": 1}
 _GATE = {"none": 0, "sigmoid": 1, "silu": 2}
@@ -96,6 +99,11 @@ class _MatrixStateMixer:
         self.norm_weight = rt.vector(weights[n["norm"]])
         self.o = Linear(weights[n["o"]], rt)
         self.out_scale = 1.0
+        # prompts: chunks over many CTAs where the head sizes allow and the projections are 16-bit (the running
+        # sums of logarithms the chunks work with are rounding next to those, not next to 32-bit projections);
+        # GOGGUF_B200_SCAN_CHUNKED=0: token by token everywhere, the form of decode steps
+        self._chunked = (os.environ.get("GOGGUF_B200_SCAN_CHUNKED", "1") != "0" and rt.dtype != torch.float32
+                         and max(self.d, self.dv) <= K.SCAN_CHUNKS_MAX_HEAD)
         return n
 
     def scale_output(self, mult: float) -> bool:
@@ -103,8 +111,19 @@ class _MatrixStateMixer:
         self.out_scale = float(mult)
         return True
 
-    def _scan(self, x, raw, cache, ctx) -> None:
+    def _gate_args(self) -> Dict[str, object]:
         raise NotImplementedError
+
+    def _scan(self, x, raw, cache, ctx) -> None:
+        T, H, d, dv = ctx.n_tokens, self.H, self.d, self.dv
+        if self._chunked and ctx.max_new >= CHUNKED_FROM:
+            n = K.gated_scan_chunks_scratch(T, ctx.n_seqs, H, d, dv)
+            K.gated_scan_chunks(x, self.off["q"], self.off[self.rows[1]], self.off["v"], raw,
+                                ctx.ws.get("recurrence_chunk_states", (n,), torch.float32), cache.state, ctx.cu_seqlens,
+                                ctx.slots, ctx.seq_of_token, T, ctx.n_seqs, H, d, dv, **self._gate_args())
+            return
+        K.gated_scan(x, self.off["q"], self.off[self.rows[1]], self.off["v"], raw, cache.state, ctx.cu_seqlens, ctx.slots,
+                     ctx.seq_of_token, T, ctx.n_seqs, H, d, dv, **self._gate_args())
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext, cache: StateView,
                 writes_cache: bool = True) -> None:
@@ -149,10 +168,8 @@ class LightningMixer(_MatrixStateMixer):
             raise ValueError("lightning: every decay must lie in [0, 1]")
         self.decay = torch.tensor(decay, dtype=torch.float32, device=rt.device)
 
-    def _scan(self, x, raw, cache, ctx) -> None:
-        K.gated_scan(x, self.off["q"], self.off["k"], self.off["v"], raw, cache.state, ctx.cu_seqlens, ctx.slots,
-                     ctx.seq_of_token, ctx.n_tokens, ctx.n_seqs, self.H, self.d, self.dv, decay=self.decay,
-                     act_q=self.act_q, act_k=self.act_k, act_v=self.act_v)
+    def _gate_args(self) -> Dict[str, object]:
+        return dict(decay=self.decay, act_q=self.act_q, act_k=self.act_k, act_v=self.act_v)
 
 
 @register_mixer("hgrn2")
@@ -181,7 +198,5 @@ class Hgrn2Mixer(_MatrixStateMixer):
         self.f_bias = rt.vector(weights[n["f_bias"]])
         self.lower = rt.vector(weights[n["lower"]])
 
-    def _scan(self, x, raw, cache, ctx) -> None:
-        K.gated_scan(x, self.off["q"], self.off["f"], self.off["v"], raw, cache.state, ctx.cu_seqlens, ctx.slots,
-                     ctx.seq_of_token, ctx.n_tokens, ctx.n_seqs, self.H, self.d, self.dv, forget_bias=self.f_bias,
-                     forget_lower=self.lower, act_q=self.act_q, act_v=self.act_v)
+    def _gate_args(self) -> Dict[str, object]:
+        return dict(forget_bias=self.f_bias, forget_lower=self.lower, act_q=self.act_q, act_v=self.act_v)

@@ -82,7 +82,7 @@ def every_expert(cfg: dict) -> dict:
 
 
 CASES = {"S": (CASE_S, 3), "ONE": (CASE_ONE, 4), "W": (CASE_W, 6)}
-CASES.update({"SB": (every_expert(CASE_S), 3), "WB": (every_expert(CASE_W), 6)})
+CASES.update({"SB": (every_expert(CASE_S), 3), "ONEB": (every_expert(CASE_ONE), 4), "WB": (every_expert(CASE_W), 6)})
 
 
 def make_folder(tmp, name: str, store_dtype: str = "float32", std: float = 0.12, norm_std: float = 0.1) -> str:

@@ -19,20 +19,25 @@ TOL_BF16 = 4e-2      # as for the other architectures (tests/helpers.py): roundi
 DEV = "cuda:0"
 
 
-def close(got, want, dtype, own32=None, few=True) -> bool:
+def close(got, want, dtype, own32=None, few=True, gauge=None) -> bool:
     """float32: every row within TOL_F32, or within three times the distance `own32` of the plain implementation run
     in float32 from the same implementation in float64 where that is larger.  bfloat16: every row within TOL_BF16,
     except that (`few`) among 25 rows and more one in 25 may lie up to three times further out while the median
     stays below half the bound: the norms after the heads divide by the root mean square of as few as eight numbers,
     and where those nearly cancel, rounding alone moves the row; with routed experts, two choice scores closer than
     the rounding of the activations let the bfloat16 run take the other expert.  Each kernel alone, the float32 runs
-    and the made-up weights hold every row."""
+    and the made-up weights hold every row.  `gauge` (bfloat16): the same rows from another run of the product (the
+    prompt in one piece), itself held to the bound above; a row that rounding has moved there by d may lie up to 3 d
+    out here: another cut of the prompt adds in another order, and such a row shows it as much."""
     got, want = got.double().cpu(), want.double().cpu()
     scale = want.abs().max().clamp_min(1e-30)
     rows = (got - want).abs().reshape(got.shape[0], -1).max(dim=1).values / scale
     bound = TOL_F32 if dtype == "float32" else TOL_BF16
     if own32 is not None and dtype == "float32":
         bound = max(bound, 3.0 * rel_err(own32, want))
+    if gauge is not None and dtype == "bfloat16":
+        g = (gauge.double().cpu() - want).abs().reshape(got.shape[0], -1).max(dim=1).values / scale
+        rows = rows * (bound / torch.maximum(3.0 * g, torch.full_like(g, bound)))
     bad = int((rows >= bound).sum())
     ok = bad == 0 or (few and dtype == "bfloat16" and got.shape[0] >= 25 and bad <= got.shape[0] // 25
                       and float(rows.median()) < bound / 2 and float(rows.max()) < 3 * bound)
@@ -83,7 +88,7 @@ def _batch(lens):
 
 # ----------------------------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,taps", [(80, 4), (64, 1), (256, 2), (24, 7)])
+@pytest.mark.parametrize("W,taps", [(80, 4), (64, 1), (256, 2), (24, 7), (36, 3), (50, 4), (32, 9)])
 def test_input_convolution_alone(dt, W, taps):
     """Two sequences in one batch; whole, then in portions down to one and two tokens with the tail carried in the
     state, in slots that were used before and hold leftovers until they are opened."""
@@ -106,7 +111,9 @@ def test_input_convolution_alone(dt, W, taps):
             h = torch.cat([rows[b][at[b]:at[b] + n] for b, n in zip(live, ns)]).to(DEV).contiguous()
             out = torch.empty_like(h)
             cu, sot = _batch(ns)
-            K.short_conv(h, out, c.to(DEV), state, cu, _i32([slots[b] for b in live]), sot, h.shape[0], len(live))
+            # (steps of single tokens say so and take the launch that also moves the state on; every other time not)
+            K.short_conv(h, out, c.t().contiguous().to(DEV), state, cu, _i32([slots[b] for b in live]), sot, h.shape[0], len(live),
+                         max_new=max(ns) if k % 2 == 0 else 0)
             o = 0
             for b, n in zip(live, ns):
                 got[b].append(out[o:o + n].cpu())
@@ -204,6 +211,74 @@ def test_matrix_state_recurrences_alone(dt, kind, H, d, dv):
                 at[b] += n
         got = torch.cat([torch.cat(x) for x in got])
         assert rel_err(got, want) < (2e-5 if dt == torch.float32 else 1.2e-2), (kind, cuts)
+    assert torch.all(state[[1, 3]] == 3.0)
+
+
+def _scan_raw_reference(kind, x, H, d, dv, consts, S0):
+    """o_t before the norm and the state after the last token, from the state S0 [H, d, dv], in float64."""
+    n = x.shape[0]
+    q = plain.silu(x[:, :H * d]).view(n, H, d)
+    if kind == "lightning":
+        k = plain.silu(x[:, H * d:2 * H * d]).view(n, H, d)
+        v = plain.silu(x[:, 2 * H * d:2 * H * d + H * dv]).view(n, H, dv)
+        g = torch.tensor(consts["decay"], dtype=x.dtype)[None, :, None].expand(n, H, d)
+    else:
+        g = (consts["lower"] + (1 - consts["lower"]) * plain.sigmoid(x[:, H * d:2 * H * d] + consts["bias"])).view(n, H, d)
+        k = 1 - g
+        v = x[:, 2 * H * d:2 * H * d + H * dv].view(n, H, dv)
+    S = S0.clone()
+    o = torch.zeros(n, H, dv, dtype=x.dtype)
+    for t in range(n):
+        S = g[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return o.reshape(n, H * dv), S
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind,H,d,dv,harsh", [("lightning", 3, 24, 40, False), ("hgrn2", 2, 20, 36, False),
+                                               ("lightning", 2, 128, 64, False), ("hgrn2", 2, 64, 128, True),
+                                               ("hgrn2", 1, 128, 128, False), ("hgrn2", 3, 96, 8, True),
+                                               ("lightning", 1, 32, 128, False)])
+def test_matrix_state_recurrences_in_chunks(dt, kind, H, d, dv, harsh):
+    """Prompts through the form that cuts them into chunks for many CTAs, against the plain loop: portions that end
+    on a chunk's border, one token past it and well inside; a second portion from the carried state; unequal
+    sequences side by side with one of a single token; a padding row; forget gates that close almost entirely
+    (harsh), where the products of gates inside a chunk fall below what float32 holds."""
+    K = _K()
+    g = torch.Generator().manual_seed(H * 1000 + d + dv)
+    width = 2 * H * d + 2 * H * dv
+    lens = [203, 65, 1, 130]
+    rows = [(torch.randn(n, width, generator=g) * (2.0 if harsh else 1.0)).to(dt) for n in lens]
+    consts = dict(decay=[1.0, 0.97, 0.5][:H] if H > 1 else [0.995],
+                  lower=(torch.rand(H * d, generator=g) * (1e-3 if harsh else 1.0)).double(),
+                  bias=(torch.randn(H * d, generator=g) - (6.0 if harsh else 0.0)).double())
+    kw = (dict(decay=torch.tensor(consts["decay"], device=DEV), act_k=1, act_v=1) if kind == "lightning" else
+          dict(forget_bias=consts["bias"].float().to(DEV), forget_lower=consts["lower"].float().to(DEV)))
+    state = torch.full((6, H, d, dv), 3.0, device=DEV)
+    slots = [4, 0, 5, 2]
+    state[slots] = 0
+    S = [torch.zeros(H, d, dv, dtype=torch.float64) for _ in lens]
+    at = [0] * len(lens)
+    for ns in ([64, 65, 1, 0], [129, 0, 0, 64], [10, 0, 0, 66]):
+        live = [b for b, n in enumerate(ns) if n]
+        x = torch.cat([rows[b][at[b]:at[b] + ns[b]] for b in live] + [torch.zeros(1, width).to(dt)]).to(DEV).contiguous()
+        T = x.shape[0]
+        cu = _i32([0] + list(torch.tensor([ns[b] for b in live]).cumsum(0)) + [T])
+        sot = _i32([i for i, b in enumerate(live) for _ in range(ns[b])] + [-1])
+        sl = _i32([slots[b] for b in live] + [1])
+        raw = torch.full((T, H * dv), 7.0, device=DEV)
+        n_seqs = len(live) + 1
+        scratch = torch.empty(K.gated_scan_chunks_scratch(T, n_seqs, H, d, dv), device=DEV)
+        K.gated_scan_chunks(x, 0, H * d, 2 * H * d, raw, scratch, state, cu, sl, sot, T, n_seqs, H, d, dv, act_q=1, **kw)
+        o = 0
+        for b in live:
+            want, S[b] = _scan_raw_reference(kind, rows[b][at[b]:at[b] + ns[b]].double(), H, d, dv, consts, S[b])
+            got = raw[o:o + ns[b]].cpu()
+            # (running sums of log2 g reach hundreds where the gates close: their rounding is the looser bound)
+            assert rel_err(got, want) < (1e-4 if harsh else 2e-5), (kind, ns, b)
+            assert rel_err(state[slots[b]].cpu(), S[b]) < (1e-4 if harsh else 2e-5), (kind, ns, b)
+            o += ns[b]
+            at[b] += ns[b]
     assert torch.all(state[[1, 3]] == 3.0)
 
 
@@ -332,14 +407,16 @@ def test_portions_and_decoding_equal_the_whole_prompt(tmp_path_factory, name, dt
     tokens = random_tokens(cfg["vocab"], 171, seed=12)
     want = plain_logits(cfg, w, tokens)
     m, cache, st = load(folder, dtype)
-    for cuts in ([171], [64, 64, 43], [2, 2, 61, 3, 100], [63, 2, 70], [130], [1, 65, 2, 2], [1, 1, 1, 3, 160]):
+    whole = None
+    for cuts in ([171], [64, 64, 43], [2, 2, 61, 3, 100], [63, 2, 70], [130], [1, 65, 2, 2], [1, 129, 41], [1, 1, 1, 3, 160]):
         got = run_cut(st, cache, tokens, cuts)
-        assert close(got, want, dtype), (rel_err(got, want), name, cuts)
+        assert close(got, want, dtype, gauge=whole), (rel_err(got, want), name, cuts)
+        whole = got if whole is None else whole
     # token by token from the first one, through captured graphs: the first tokens of a sequence, the convolution's
     # zeros before its start, states that start empty
     _, cache_g, st_g = load(folder, dtype, graphs=True)
     got = run_cut(st_g, cache_g, tokens[:90], [])
-    assert close(got, want[:90], dtype), rel_err(got, want[:90])
+    assert close(got, want[:90], dtype, gauge=whole[:90]), rel_err(got, want[:90])
     assert st_g.replays >= 89
 
 
