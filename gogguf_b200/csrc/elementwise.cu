@@ -848,17 +848,15 @@ __global__ void __launch_bounds__(256) short_conv_state_kernel(const T* h, float
 // its sequence's state there, and it moves the state on itself (no second launch).
 template <typename T> struct ConvRow;
 template <> struct ConvRow<float> {
-    static __device__ __forceinline__ void load(const float* p, float* v) {
-        const float4 a = *reinterpret_cast<const float4*>(p);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    static __device__ __forceinline__ void unpack(const uint4& a, float* v) {
+        v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
     }
-    static __device__ __forceinline__ void store(float* p, const float* v) {
-        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    static __device__ __forceinline__ uint4 pack(const float* v) {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
     }
 };
 template <> struct ConvRow<bf16> {
-    static __device__ __forceinline__ void load(const bf16* p, float* v) {
-        const uint4 a = *reinterpret_cast<const uint4*>(p);
+    static __device__ __forceinline__ void unpack(const uint4& a, float* v) {
         const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&a);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -866,17 +864,29 @@ template <> struct ConvRow<bf16> {
             v[2 * i] = f.x; v[2 * i + 1] = f.y;
         }
     }
-    static __device__ __forceinline__ void store(bf16* p, const float* v) {
+    static __device__ __forceinline__ uint4 pack(const float* v) {
         uint4 a;
         __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&a);
 #pragma unroll
         for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        *reinterpret_cast<uint4*>(p) = a;
+        return a;
     }
 };
+static __device__ __forceinline__ void conv_load4(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+static __device__ __forceinline__ void conv_store4(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
 
-template <typename T, int TAPS>
-__global__ void __launch_bounds__(256) short_conv_vec_kernel(const T* h, T* out, const float* __restrict__ w, float* state,
+// A thread makes V channels of TT consecutive rows of the step.  The TT rows and the taps - 1 rows before them are
+// asked for before anything is known of the tokens' sequences (they are rows of this step's h whatever sequence
+// they belong to), so that one round of memory latency serves them, the weights and the sequences' bounds together;
+// a row from before a sequence's start in this step is then replaced by the state's.  Blocks (TT rows, 128 x V
+// channels).
+template <typename T, int TAPS, int TT>
+__global__ void __launch_bounds__(128) short_conv_vec_kernel(const T* h, T* out, const float* __restrict__ w, float* state,
                                                              const int* __restrict__ cu_seqlens,
                                                              const int* __restrict__ slots,
                                                              const int* __restrict__ seq_of_token, int W, int ntok,
@@ -885,71 +895,80 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(const T* h, T* out,
     pdl_wait();
     constexpr int V = 16 / (int)sizeof(T);
     constexpr int R = TAPS - 1;
-    const int per_row = W / V;
-    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (item >= (long long)ntok * per_row) return;
-    int t, c0;
-    if ((long long)ntok * per_row < (1ll << 31)) {
-        t = (int)((unsigned)item / (unsigned)per_row);
-        c0 = (int)((unsigned)item % (unsigned)per_row) * V;
-    } else {
-        t = (int)(item / per_row);
-        c0 = (int)(item % per_row) * V;
-    }
-    const int b = seq_of_token[t];
-    T* o = out + (size_t)t * W + c0;
-    float acc[V], x[V];
-    if (b < 0) {
+    const int c0 = (blockIdx.y * 128 + threadIdx.x) * V;
+    if (c0 >= W) return;
+    const int t0 = blockIdx.x * TT;
+    uint4 row[R + TT];                                    // rows t0 - R .. t0 + TT - 1 of h
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v] = 0.f;
-        ConvRow<T>::store(o, acc);
-        return;
+    for (int i = 0; i < R + TT; ++i) {
+        const int s = t0 - R + i;
+        row[i] = (s >= 0 && s < ntok) ? *reinterpret_cast<const uint4*>(h + (size_t)s * W + c0) : make_uint4(0u, 0u, 0u, 0u);
     }
+    int seq[TT];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) seq[tt] = t0 + tt < ntok ? seq_of_token[t0 + tt] : -1;
     float wr[TAPS * V];                                   // tap j of channel c0 + v at [j * V + v]
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) {
 #pragma unroll
-        for (int v = 0; v < V; v += 4) ConvRow<float>::load(w + (size_t)j * W + c0 + v, wr + j * V + v);
+        for (int v = 0; v < V; v += 4) conv_load4(w + (size_t)j * W + c0 + v, wr + j * V + v);
     }
-    ConvRow<T>::load(h + (size_t)t * W + c0, x);
 #pragma unroll
-    for (int v = 0; v < V; ++v) acc[v] = x[v] * (keep + wr[R * V + v]);
-    if (R > 0) {
-        const int start = cu_seqlens[b];
-        float* st = state + (size_t)slots[b] * R * W + c0;
+    for (int tt = 0; tt < TT; ++tt) {
+        const int t = t0 + tt;
+        if (t >= ntok) break;
+        T* o = out + (size_t)t * W + c0;
+        const int b = seq[tt];
+        if (b < 0) {
+            *reinterpret_cast<uint4*>(o) = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
+        float acc[V], x[V];
+        ConvRow<T>::unpack(row[R + tt], x);
 #pragma unroll
-        for (int j = 0; j < R; ++j) {
-            const int s = t - R + j;
-            float prev[V];
-            if (s >= start) {
-                ConvRow<T>::load(h + (size_t)s * W + c0, prev);
-            } else {
-                const float* sr = st + (size_t)(R + (s - start)) * W;
+        for (int v = 0; v < V; ++v) acc[v] = x[v] * (keep + wr[R * V + v]);
+        if (R > 0) {
+            const int start = cu_seqlens[b];
+            float* st = t - R < start ? state + (size_t)slots[b] * R * W + c0 : nullptr;
 #pragma unroll
-                for (int v = 0; v < V; v += 4) ConvRow<float>::load(sr + v, prev + v);
+            for (int j = 0; j < R; ++j) {
+                const int s = t - R + j;
+                float prev[V];
+                if (s >= start) {
+                    ConvRow<T>::unpack(row[tt + j], prev);
+                } else {
+                    const float* sr = st + (size_t)(R + (s - start)) * W;
+#pragma unroll
+                    for (int v = 0; v < V; v += 4) conv_load4(sr + v, prev + v);
+                }
+#pragma unroll
+                for (int v = 0; v < V; ++v) acc[v] = fmaf(wr[j * V + v], prev[v], acc[v]);
+                // one token of this sequence: row j of the old state was just read (s - start = j - R); it is row
+                // j - 1 of the new one, which this thread read in the round before
+                if (one_each && j >= 1) {
+#pragma unroll
+                    for (int v = 0; v < V; v += 4) conv_store4(st + (size_t)(j - 1) * W + v, prev + v);
+                }
             }
+            if (one_each) {
 #pragma unroll
-            for (int v = 0; v < V; ++v) acc[v] = fmaf(wr[j * V + v], prev[v], acc[v]);
-            // one token of this sequence: row j of the old state was just read (s - start = j - R); it is row j - 1
-            // of the new one, which this thread read in the round before
-            if (one_each && j >= 1) {
-#pragma unroll
-                for (int v = 0; v < V; v += 4) ConvRow<float>::store(st + (size_t)(j - 1) * W + v, prev + v);
+                for (int v = 0; v < V; v += 4) conv_store4(st + (size_t)(R - 1) * W + v, x + v);
             }
         }
-        if (one_each) {
-#pragma unroll
-            for (int v = 0; v < V; v += 4) ConvRow<float>::store(st + (size_t)(R - 1) * W + v, x + v);
-        }
+        *reinterpret_cast<uint4*>(o) = ConvRow<T>::pack(acc);
     }
-    ConvRow<T>::store(o, acc);
 }
 
+// Few rows (decode steps): a row a thread, so that the step fills more of the GPU; else four.
 template <typename T, int TAPS>
 static int short_conv_vec_launch(const T* h, T* out, const float* w, float* state, const int* cu_seqlens, const int* slots,
                                  const int* seq_of_token, int ntok, int W, float keep, int one_each, cudaStream_t stream) {
-    const long long items = (long long)ntok * (W / (16 / (int)sizeof(T)));
-    return gg_launch(short_conv_vec_kernel<T, TAPS>, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, stream, 1, h, out,
+    constexpr int V = 16 / (int)sizeof(T);
+    const unsigned cb = (unsigned)((W / V + 127) / 128);
+    if (ntok < 1024)
+        return gg_launch(short_conv_vec_kernel<T, TAPS, 1>, dim3((unsigned)ntok, cb), dim3(128), 0, stream, 1, h, out, w,
+                         state, cu_seqlens, slots, seq_of_token, W, ntok, keep, one_each);
+    return gg_launch(short_conv_vec_kernel<T, TAPS, 4>, dim3((unsigned)((ntok + 3) / 4), cb), dim3(128), 0, stream, 1, h, out,
                      w, state, cu_seqlens, slots, seq_of_token, W, ntok, keep, one_each);
 }
 
@@ -975,7 +994,7 @@ GG_API gg_short_conv(const void* h, void* out, int dtype, const float* w, float*
     const int cb = min((W + 255) / 256, 65535);
     const int one_each = max_new == 1;
     GG_DISPATCH_DTYPE(dtype, T,
-        const bool vec = taps <= CONV_VEC_MAX_TAPS && W % (16 / (int)sizeof(T)) == 0 && ((uintptr_t)h | (uintptr_t)out | (uintptr_t)w |
+        const bool vec = taps <= CONV_VEC_MAX_TAPS && W / 4 <= 65535 * 128 && W % (16 / (int)sizeof(T)) == 0 && ((uintptr_t)h | (uintptr_t)out | (uintptr_t)w |
                                                                           (uintptr_t)state) % 16 == 0;
         if (vec) {
             short_conv_vec<T>(taps, (const T*)h, (T*)out, w, state, cu_seqlens, slots, seq_of_token, ntok, W, keep, one_each,

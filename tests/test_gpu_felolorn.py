@@ -88,19 +88,25 @@ def _batch(lens):
 
 # ----------------------------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,taps", [(80, 4), (64, 1), (256, 2), (24, 7), (36, 3), (50, 4), (32, 9)])
-def test_input_convolution_alone(dt, W, taps):
+@pytest.mark.parametrize("W,taps,lens", [(80, 4, (37, 9)), (64, 1, (37, 9)), (256, 2, (37, 9)), (24, 7, (37, 9)),
+                                         (36, 3, (37, 9)), (50, 4, (37, 9)), (32, 9, (37, 9)),
+                                         (1032, 4, (1101, 9)), (24, 5, (1030, 3)), (40, 1, (1300, 2))])
+def test_input_convolution_alone(dt, W, taps, lens):
     """Two sequences in one batch; whole, then in portions down to one and two tokens with the tail carried in the
-    state, in slots that were used before and hold leftovers until they are opened."""
+    state, in slots that were used before and hold leftovers until they are opened.  Steps of a thousand rows and
+    more take the form that makes four rows a thread: a sequence's start in the middle of such a group, rows that
+    do not fill the last group, channels that do not fill the last block."""
     K = _K()
     g = torch.Generator().manual_seed(W + taps)
-    lens = [37, 9]
+    lens = list(lens)
     rows = [torch.randn(n, W, generator=g).to(dt) for n in lens]
     c = (0.5 * torch.randn(W, taps, generator=g)).float()
     want = torch.cat([r.double() + plain.causal_taps(r.double(), c.double()) for r in rows])
     state = torch.full((5, max(taps - 1, 1), W), 7.0, device=DEV)[:, :taps - 1] if taps > 1 else None
     slots = [3, 1]
-    for cuts in ([[37], [9]], [[1, 2, 30, 4], [2, 1, 1, 5]], [[1] * 37, [1] * 9]):
+    na, nb = lens
+    for cuts in ([[na], [nb]], [[1, 2, na - 7, 4], [2, 1, 1, nb - 4]] if nb >= 9 else [[2, na - 2], [1, nb - 1]],
+                 [[1] * min(na, 40) + [na - 40] * (na > 40), [1] * nb]):
         if state is not None:
             state[slots] = 0                       # what opening a slot does
         got = [[], []]
