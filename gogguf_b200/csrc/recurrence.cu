@@ -199,14 +199,125 @@ __global__ void __launch_bounds__(256) scan_finish_kernel(const float* raw, cons
     }
 }
 
+// The same with four neighbouring outputs a thread (16-byte reads of the float32 rows, 8- or 16-byte reads of the
+// gate and stores), the row held in registers between the sum of squares and the store: rows of up to 4,096 numbers
+// (whole) or heads of up to 512 (a warp a head), every extent a multiple of four.
+template <typename T> struct Fin4;
+template <> struct Fin4<float> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Fin4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float* v) {
+        const uint2 a = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float* v) {
+        uint2 a;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&a);
+        h2[0] = __floats2bfloat162_rn(v[0], v[1]);
+        h2[1] = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(p) = a;
+    }
+};
+
+#define FIN_K 4
+template <typename T>
+__device__ __forceinline__ void fin_emit(const float* v, float f, const float* __restrict__ w, const T* gp, T* o, int c,
+                                         int wc, int gate) {
+    float r[4], g[4], wv[4] = {1.f, 1.f, 1.f, 1.f};
+    if (w != nullptr) Fin4<float>::load(w + wc, wv);
+    if (gate) Fin4<T>::load(gp + c, g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        r[i] = v[i] * f * wv[i];
+        if (gate == 1) r[i] *= rec_sigmoid(g[i]);
+        else if (gate == 2) r[i] *= g[i] * rec_sigmoid(g[i]);
+    }
+    Fin4<T>::store(o + c, r);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) scan_finish_vec_kernel(const float* raw, const T* x, long long ld, int g_off, T* out,
+                                                              const float* __restrict__ w,
+                                                              const int* __restrict__ seq_of_token, int H, int dv, float eps,
+                                                              float out_scale, int whole, int gate) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const int n = H * dv;
+    const float* r = raw + (size_t)t * n;
+    T* o = out + (size_t)t * n;
+    const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+    if (seq_of_token[t] < 0) {
+        for (int c = 4 * threadIdx.x; c < n; c += 4 * blockDim.x) Fin4<T>::store(o + c, zero);
+        return;
+    }
+    const T* gp = x + (size_t)t * ld + g_off;
+    float v[FIN_K][4];
+    if (whole) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < FIN_K; ++k) {
+            const int c = 4 * (threadIdx.x + 256 * k);
+            if (c < n) {
+                Fin4<float>::load(r + c, v[k]);
+                ss += v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
+            }
+        }
+        ss = block_sum(ss, red);
+        const float f = out_scale / sqrtf(ss / (float)n + eps);
+#pragma unroll
+        for (int k = 0; k < FIN_K; ++k) {
+            const int c = 4 * (threadIdx.x + 256 * k);
+            if (c < n) fin_emit<T>(v[k], f, w, gp, o, c, c, gate);
+        }
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int h = warp; h < H; h += 8) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < FIN_K; ++k) {
+            const int c = 4 * (lane + 32 * k);
+            if (c < dv) {
+                Fin4<float>::load(r + h * dv + c, v[k]);
+                ss += v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
+            }
+        }
+        ss = warp_sum(ss);
+        const float f = out_scale / sqrtf(ss / (float)dv + eps);
+#pragma unroll
+        for (int k = 0; k < FIN_K; ++k) {
+            const int c = 4 * (lane + 32 * k);
+            if (c < dv) fin_emit<T>(v[k], f, w, gp, o, h * dv + c, c, gate);
+        }
+    }
+}
+
 GG_API gg_scan_finish(const float* raw, const void* x, int dtype, long long ld, int g_off, void* out, const float* w,
                       const int* seq_of_token, int ntok, int H, int dv, float eps, float out_scale, int whole, int gate,
                       cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (H <= 0 || dv <= 0 || gate < 0 || gate > 2 || (gate != 0 && x == nullptr)) return GG_ERR_ARG;
+    const bool fits = dv % 4 == 0 && (whole ? (long long)H * dv <= 4 * 256 * FIN_K : dv <= 4 * 32 * FIN_K);
+    const bool gate_ok = gate == 0 || (ld % 4 == 0 && g_off % 4 == 0 && ((uintptr_t)x & 15) == 0);
+    const bool vec = fits && gate_ok && (((uintptr_t)raw | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
     GG_DISPATCH_DTYPE(dtype, T,
-        gg_launch(scan_finish_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, raw, (const T*)x, ld, g_off, (T*)out, w,
-                  seq_of_token, H, dv, eps, out_scale, whole, gate));
+        if (vec)
+            gg_launch(scan_finish_vec_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, raw, (const T*)x, ld, g_off, (T*)out, w,
+                      seq_of_token, H, dv, eps, out_scale, whole, gate);
+        else
+            gg_launch(scan_finish_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, raw, (const T*)x, ld, g_off, (T*)out, w,
+                      seq_of_token, H, dv, eps, out_scale, whole, gate));
     return gg_last_error();
 }
 

@@ -176,17 +176,21 @@ def _scan_reference(kind, x, H, d, dv, consts, eps):
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("kind,H,d,dv", [("lightning", 3, 24, 40), ("hgrn2", 2, 20, 36), ("lightning", 2, 128, 64),
-                                         ("hgrn2", 4, 64, 128), ("hgrn2", 1, 72, 8), ("lightning", 1, 16, 16)])
+                                         ("hgrn2", 4, 64, 128), ("hgrn2", 1, 72, 8), ("lightning", 1, 16, 16),
+                                         ("lightning", 2, 8, 6), ("hgrn2", 3, 12, 10), ("hgrn2", 1, 8, 516),
+                                         ("lightning", 9, 4, 460), ("hgrn2", 9, 4, 132)])
 def test_matrix_state_recurrences_alone(dt, kind, H, d, dv):
     """Made-up projections of two requests through the scan and its finish against the plain loops: whole, then in
-    portions and token by token from the carried state, in slots that held another sequence before."""
+    portions and token by token from the carried state, in slots that held another sequence before.  Value sizes
+    that are no multiple of four, heads of more than 512 values and rows of more than 4,096 take the finish kernel's
+    plain form, more heads than a CTA has warps its loop over heads."""
     K = _K()
     g = torch.Generator().manual_seed(H * 100 + d)
     eps = 1e-5
     lens = [75, 11]
     width = 2 * H * d + (2 if kind == "lightning" else 1) * H * dv
     rows = [torch.randn(n, width, generator=g).to(dt) for n in lens]
-    consts = dict(decay=[1.0, 0.97, 0.5, 0.0][:H] if H > 1 else [0.995],
+    consts = dict(decay=([1.0, 0.97, 0.5, 0.0] * 3)[:H] if H > 1 else [0.995],
                   norm=(1 + 0.2 * torch.randn(H * dv if kind == "lightning" else dv, generator=g)).double(),
                   lower=torch.rand(H * d, generator=g).double(), bias=torch.randn(H * d, generator=g).double())
     want = torch.cat([_scan_reference(kind, r.double(), H, d, dv, consts, eps) for r in rows])
