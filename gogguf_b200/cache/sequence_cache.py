@@ -14,6 +14,10 @@ What each scheduled layer needs is asked of its mixer as a *request*:
 * `StateRequest(shape, dtype)` - a fixed-size state per sequence, ``[max_slots, *shape]`` for that
   layer, zeroed when a slot is opened.
 * None - the layer keeps nothing.
+* `SharedView(entry, member, expects)` - no storage: the mixer is handed the view that an earlier schedule entry's
+  request (member `member` of it, where that request is a tuple) was given, and reads what that entry writes.
+  It may stand alone or as a member of a tuple, so that a layer shares its keys and values with an earlier layer
+  while the rest of its state is its own.
 * a tuple of requests - a mixer made of several mixers asks for one cache or state per member; each
   member's request is grouped and stored as if a layer of its own had made it, and the layer is
   handed the tuple of their views.
@@ -60,6 +64,16 @@ class KVRequest:
 class StateRequest:
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class SharedView:
+    """The view of an earlier schedule entry's request instead of storage of one's own.  `member` picks a member
+    where that entry's request is a tuple (None: the entry's whole view).  `expects` (optional) is the request the
+    reader would have made itself; the source's request must equal it."""
+    entry: int
+    member: Optional[int] = None
+    expects: Optional[object] = None
 
 
 Request = Optional[object]       # an instance of any registered request class, or None
@@ -347,6 +361,7 @@ class SequenceCache:
         member_views: Dict[object, object] = {}
         tuples: Dict[int, int] = {}
         single: Dict[object, object] = {}
+        borrowed: Dict[object, SharedView] = {}
         for i, (rq, src) in enumerate(zip(requests, cache_of)):
             if src is not None:
                 continue
@@ -361,6 +376,22 @@ class SequenceCache:
             for entry, r in members:
                 if r is None:
                     member_views[entry] = None
+                    continue
+                if isinstance(r, SharedView):
+                    if not (0 <= r.entry < i) or cache_of[r.entry] is not None:
+                        raise CacheError(f"schedule entry {i}: a shared view must name an earlier entry that owns its "
+                                         f"cache, not {r.entry}")
+                    theirs = requests[r.entry]
+                    if r.member is not None:
+                        if not isinstance(theirs, (tuple, list)) or not (0 <= r.member < len(theirs)):
+                            raise CacheError(f"schedule entry {i}: entry {r.entry} has no member {r.member}")
+                        theirs = theirs[r.member]
+                    if theirs is None or isinstance(theirs, (tuple, list, SharedView)):
+                        raise CacheError(f"schedule entry {i}: entry {r.entry} has no storage of its own to share there")
+                    if r.expects is not None and theirs != r.expects:
+                        raise CacheError(f"schedule entry {i} expects {r.expects} of entry {r.entry}, which asked for "
+                                         f"{theirs}")
+                    borrowed[entry] = r
                     continue
                 store_cls = STORES.get(type(r))
                 if store_cls is None:
@@ -383,6 +414,8 @@ class SequenceCache:
                 self.groups.append(st)
             for e in entries:
                 member_views[e] = st.view(e)
+        for e, r in borrowed.items():
+            member_views[e] = member_views[r.entry if r.member is None else (r.entry, r.member)]
         for e, v in member_views.items():
             if not isinstance(e, tuple):
                 self._views[e] = v

@@ -58,6 +58,8 @@ MODULES: Dict[str, str] = {
     "moe": "moe.cu",
     "retention": "retention.cu",
     "recurrence": "recurrence.cu",
+    "diag_recurrence": "diag_recurrence.cu",
+    "diff_attention": "diff_attention.cu",
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_fast": "attention_fast.cu",

@@ -1052,5 +1052,312 @@ GG_API gg_softcap(float* z, float cap, long long n, cudaStream_t stream) {
     return gg_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, z, cap, n);
 }
 
+// ----------------------------------------------------------------------------- RMS norm in groups
+// A row of H numbers is cut into `groups` equal consecutive runs; each run is divided by its own
+// sqrt(mean(run^2) + eps) and the whole is multiplied by w [H].  groups = 1 is the plain RMS norm.
+// Norm of gathered float32 rows into the compute dtype (the model's last norm): one block per row.
+template <typename T>
+__global__ void __launch_bounds__(256) group_rmsnorm_kernel(const float* x, const int* __restrict__ rows,
+                                                            const float* __restrict__ w, T* out, int H, int groups, float eps) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows != nullptr ? rows[r] : r;
+    T* o = out + (size_t)r * H;
+    if (src < 0) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<T>(0.f);
+        return;
+    }
+    const float* xr = x + (size_t)src * H;
+    const int gs = H / groups;
+    for (int g = 0; g < groups; ++g) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = xr[g * gs + i]; ss = fmaf(v, v, ss); }
+        ss = block_sum(ss, red);
+        const float f = 1.0f / sqrtf(ss / (float)gs + eps);
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) o[g * gs + i] = from_f<T>(xr[g * gs + i] * f * w[g * gs + i]);
+    }
+}
+
+GG_API gg_group_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype, int R, int H, int groups,
+                        float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (H <= 0 || groups <= 0 || H % groups) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(out_dtype, T,
+        gg_launch(group_rmsnorm_kernel<T>, dim3(R), dim3(256), 0, stream, 1, x, rows, w, (T*)out, H, groups, eps));
+    return gg_last_error();
+}
+
+// x[r, :] += groupnorm(y[r, :]) * w: the norm that follows a part and the add into the stream, all float32.
+// zero_y != 0: y is left zeroed.  One block per row; a run of the row at a time.
+__global__ void __launch_bounds__(256) group_rmsnorm_add_kernel(float* x, float* y, const float* __restrict__ w, int H,
+                                                                int groups, float eps, int zero_y) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    float* yr = y + r * H;
+    float* xr = x + r * H;
+    const int gs = H / groups;
+    for (int g = 0; g < groups; ++g) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = yr[g * gs + i]; ss = fmaf(v, v, ss); }
+        ss = block_sum(ss, red);
+        const float f = 1.0f / sqrtf(ss / (float)gs + eps);
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            const int c = g * gs + i;
+            xr[c] += yr[c] * f * w[c];
+            if (zero_y) yr[c] = 0.f;
+        }
+    }
+}
+
+GG_API gg_group_rmsnorm_add(float* x, float* y, const float* w, int rows, int H, int groups, float eps, int zero_y,
+                            cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H <= 0 || groups <= 0 || H % groups) return GG_ERR_ARG;
+    gg_launch(group_rmsnorm_add_kernel, dim3(rows), dim3(256), 0, stream, 1, x, y, w, H, groups, eps, zero_y);
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- token shift
+// out[t, c] = x[t, c] + (prev[c] - x[t, c]) * mu[c], prev the row before t in its sequence: row t - 1 of the step,
+// or, for a sequence's first row of the step, state[slot] (float32 [slots][W]: the sequence's last row of the step
+// before, zeros at its start).  x is float32, out the compute dtype.  one_each != 0: no sequence brings more than
+// one row, so the thread that makes a channel is the only one that reads its state and moves it on itself;
+// otherwise token_shift_state_kernel moves the states on once every block has read them.
+template <typename T>
+__global__ void __launch_bounds__(256) token_shift_kernel(const float* x, T* out, const float* __restrict__ mu, float* state,
+                                                          const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                                                          const int* __restrict__ seq_of_token, int W, int one_each) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = seq_of_token[t];
+    T* o = out + (size_t)t * W;
+    if (b < 0) {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) o[c] = from_f<T>(0.f);
+        return;
+    }
+    const bool first = t == cu_seqlens[b];
+    float* st = state + (size_t)slots[b] * W;
+    const float* prev = first ? st : x + (size_t)(t - 1) * W;
+    const float* xr = x + (size_t)t * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = xr[c], p = prev[c];
+        o[c] = from_f<T>(v + (p - v) * mu[c]);
+        if (one_each) st[c] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256) token_shift_state_kernel(const float* x, float* state, const int* __restrict__ cu_seqlens,
+                                                                const int* __restrict__ slots,
+                                                                const int* __restrict__ seq_of_token, int W) {
+    pdl_launch();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int start = cu_seqlens[b], end = cu_seqlens[b + 1];
+    if (end <= start || seq_of_token[start] < 0) return;
+    float* st = state + (size_t)slots[b] * W;
+    const float* last = x + (size_t)(end - 1) * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) st[c] = last[c];
+}
+
+GG_API gg_token_shift(const float* x, void* out, int out_dtype, const float* mu, float* state, const int* cu_seqlens,
+                      const int* slots, const int* seq_of_token, int ntok, int n_seqs, int W, int max_new,
+                      cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (W <= 0 || state == nullptr) return GG_ERR_ARG;
+    const int one_each = max_new == 1;
+    GG_DISPATCH_DTYPE(out_dtype, T,
+        gg_launch(token_shift_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, x, (T*)out, mu, state, cu_seqlens, slots,
+                  seq_of_token, W, one_each));
+    if (!one_each)
+        gg_launch(token_shift_state_kernel, dim3(n_seqs), dim3(256), 0, stream, 1, x, state, cu_seqlens, slots, seq_of_token, W);
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- weighted sum over depth
+// hist [slots_of_depth][n] float32 keeps what every layer left; this stores x as hist[store_at] and then, if
+// n_terms > 0, replaces x by sum_{j < n_terms} coeff[j] * hist[j] (j ascending; hist[store_at] is x itself).
+__global__ void __launch_bounds__(256) depth_mix_kernel(float* hist, float* x, const float* __restrict__ coeff, int store_at,
+                                                        int n_terms, long long n) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = x[i];
+    hist[(size_t)store_at * n + i] = v;
+    if (n_terms <= 0) return;
+    float acc = 0.f;
+    for (int j = 0; j < n_terms; ++j) acc = fmaf(coeff[j], j == store_at ? v : hist[(size_t)j * n + i], acc);
+    x[i] = acc;
+}
+
+GG_API gg_depth_mix(float* hist, float* x, const float* coeff, int store_at, int n_terms, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (store_at < 0 || n_terms < 0 || (n_terms > 0 && coeff == nullptr)) return GG_ERR_ARG;
+    gg_launch(depth_mix_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, hist, x, coeff, store_at, n_terms, n);
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- float32 rows into the compute dtype
+template <typename T>
+__global__ void cast_rows_kernel(const float* x, T* out, long long n) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f<T>(x[i]);
+}
+
+GG_API gg_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    GG_DISPATCH_DTYPE(out_dtype, T,
+        gg_launch(cast_rows_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, x, (T*)out, n));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- GELU
+// out = z Phi(z), exactly (erf) or in the tanh form 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))); float32
+// arithmetic, in place allowed.
+__device__ __forceinline__ float gelu_value(float z, int tanh_form) {
+    if (tanh_form) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+}
+
+template <typename T>
+__global__ void gelu_kernel(const T* z, T* out, int tanh_form, long long n) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f<T>(gelu_value(to_f<T>(z[i]), tanh_form));
+}
+
+GG_API gg_gelu(const void* z, void* out, int dtype, int tanh_form, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(gelu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, (const T*)z, (T*)out, tanh_form, n));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- a gate per row
+// act[t, :] *= sigmoid(g . h[t, :]): one number per token, made from the token's input row h [T, W] and a stored
+// vector g [W] (float32 sum), multiplies the token's activation row act [T, F] (float32 product, rounded to the
+// dtype of act).  One block per token.
+template <typename T>
+__global__ void __launch_bounds__(256) row_gate_kernel(T* act, int F, const T* h, int W, const float* __restrict__ g,
+                                                       const int* __restrict__ seq_of_token) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    if (seq_of_token != nullptr && seq_of_token[t] < 0) return;
+    const T* hr = h + (size_t)t * W;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) s = fmaf(g[i], to_f<T>(hr[i]), s);
+    s = block_sum(s, red);
+    const float f = 1.0f / (1.0f + expf(-s));
+    T* a = act + (size_t)t * F;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) a[i] = from_f<T>(to_f<T>(a[i]) * f);
+}
+
+GG_API gg_row_gate(void* act, int F, const void* h, int W, int dtype, const float* g, const int* seq_of_token, int ntok,
+                   cudaStream_t stream) {
+    if (ntok <= 0) return 0;
+    if (F <= 0 || W <= 0 || g == nullptr) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(row_gate_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, (T*)act, F, (const T*)h, W, g, seq_of_token));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- convolution of a projection's columns
+// out[t, c] = act( bias[c] + sum_j w[j, c] * v[t - taps + 1 + j, c] ), v[s, c] = h[s, c] + in_bias[c] for rows of the
+// sequence (the last tap meets the token itself), zeros before its start; rows from before the step come from
+// state [slot][taps - 1][C] (float32: the sequence's last taps - 1 values of v).  h holds C columns of a wider
+// buffer (rows ldh apart, the compute dtype); out is float32, rows ldo apart.  act 0: none, 1: silu.  bias and
+// in_bias may be null.  Blocks (token, 256 channels).  one_each != 0: no sequence brings more than one row, so the
+// thread of a channel is the only one that reads its state and moves it on itself; otherwise
+// column_conv_state_kernel does that once every block has read the old state.
+template <typename T>
+__global__ void __launch_bounds__(256) column_conv_kernel(const T* h, long long ldh, float* out, long long ldo,
+                                                          const float* __restrict__ w, const float* __restrict__ bias,
+                                                          const float* __restrict__ in_bias, float* state,
+                                                          const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                                                          const int* __restrict__ seq_of_token, int C, int taps, int act,
+                                                          int one_each) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = seq_of_token[t];
+    float* o = out + (size_t)t * ldo;
+    if (b < 0) {
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) o[c] = 0.f;
+        return;
+    }
+    const int start = cu_seqlens[b];
+    const int R = taps - 1;
+    float* st = state + (size_t)slots[b] * R * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
+        const float cur = to_f<T>(h[(size_t)t * ldh + c]) + ib;
+        float acc = (bias != nullptr ? bias[c] : 0.f) + w[(size_t)R * C + c] * cur;
+        float carry = cur;                                 // one_each: the value that moves into the row above
+        for (int j = R - 1; j >= 0; --j) {
+            const int s = t - R + j;
+            const float v = s >= start ? to_f<T>(h[(size_t)s * ldh + c]) + ib : st[(size_t)(R + (s - start)) * C + c];
+            acc = fmaf(w[(size_t)j * C + c], v, acc);
+            if (one_each) { st[(size_t)j * C + c] = carry; carry = v; }
+        }
+        o[c] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) column_conv_state_kernel(const T* h, long long ldh, const float* __restrict__ in_bias,
+                                                                float* state, const int* __restrict__ cu_seqlens,
+                                                                const int* __restrict__ slots,
+                                                                const int* __restrict__ seq_of_token, int C, int taps) {
+    pdl_launch();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+    if (n <= 0 || seq_of_token[start] < 0) return;
+    const int R = taps - 1;
+    float* st = state + (size_t)slots[b] * R * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
+        float keep[CONV_MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j < R) {
+                const int rel = n - R + j;
+                keep[j] = rel >= 0 ? to_f<T>(h[(size_t)(start + rel) * ldh + c]) + ib : st[(size_t)(R + rel) * C + c];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)
+            if (j < R) st[(size_t)j * C + c] = keep[j];
+    }
+}
+
+// w [taps][C] float32 (a tap's weights side by side); state [slots][taps - 1][C] float32 (null only for one tap).
+GG_API gg_column_conv(const void* h, long long ldh, int dtype, float* out, long long ldo, const float* w, const float* bias,
+                      const float* in_bias, float* state, const int* cu_seqlens, const int* slots, const int* seq_of_token,
+                      int ntok, int n_seqs, int C, int taps, int act, int max_new, cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (C <= 0 || taps < 1 || taps > CONV_MAX_TAPS || (taps > 1 && state == nullptr) || act < 0 || act > 1 || ldh < C || ldo < C)
+        return GG_ERR_ARG;
+    const int cb = min((C + 255) / 256, 65535);
+    const int one_each = max_new == 1;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(column_conv_kernel<T>, dim3(ntok, cb), dim3(256), 0, stream, 1, (const T*)h, ldh, out, ldo, w, bias, in_bias,
+                  state, cu_seqlens, slots, seq_of_token, C, taps, act, one_each);
+        if (taps > 1 && !one_each)
+            gg_launch(column_conv_state_kernel<T>, dim3(n_seqs, cb), dim3(256), 0, stream, 1, (const T*)h, ldh, in_bias, state,
+                      cu_seqlens, slots, seq_of_token, C, taps));
+    return gg_last_error();
+}
+
 // 1 if this library was built with checked page tables (the debug build), else 0.
 GG_API gg_elementwise_checked() { return gg_debug_bounds(); }

@@ -53,8 +53,9 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, s
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None) -> None:
-    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x float32, weight float32, out float32/bfloat16."""
+            rows: Optional[torch.Tensor] = None, groups: int = 1) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x float32, weight float32, out float32/bfloat16.  groups > 1:
+    the row is cut into that many equal runs, each divided by its own root mean square."""
     _need(x, torch.float32, "x")
     _need(weight, torch.float32, "norm weight")
     H = x.shape[-1]
@@ -63,6 +64,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         _need(rows, torch.int32, "rows")
     if weight.numel() != H or out.shape[-1] != H or out.numel() < R * H:
         raise KernelError("rmsnorm: shapes disagree")
+    if groups > 1:
+        if H % groups:
+            raise KernelError(f"rmsnorm: {H} columns do not form {groups} equal runs")
+        kernel("elementwise", "gg_group_rmsnorm")(_p(x), _p(rows), _p(weight), _p(out), dtype_code(out.dtype), R, H,
+                                                   int(groups), float(eps), _stream())
+        return
     kernel("elementwise", "gg_rmsnorm")(_p(x), _p(rows), _p(weight), _p(out), dtype_code(out.dtype),
                                          R, H, float(eps), _stream())
 
@@ -133,7 +140,7 @@ def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Te
 
 def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
                 xhat: Optional[torch.Tensor] = None, ssq: Optional[torch.Tensor] = None, zero_y: bool = False,
-                gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> None:
+                gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None, groups: int = 1) -> None:
     """x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight, all float32.  With `gate` (float32 like y) and `gate_bias`
     (float32 [H], optional) y is first multiplied by sigmoid(gate + gate_bias), and the norm is the product's.  With `xhat` (bfloat16 like x) and `ssq`
     (float32 [rows, ceil(H / 128)]) the updated rows' bfloat16 copy and sums of squares per 128 columns are left too
@@ -144,6 +151,13 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
     H = x.shape[-1]
     if y.shape != x.shape or weight.numel() != H:
         raise KernelError("rmsnorm_add: shapes disagree")
+    if groups > 1:
+        # the norm in `groups` equal runs of the row, each over its own root mean square (no gate, no statistics)
+        if xhat is not None or gate is not None or H % groups:
+            raise KernelError("rmsnorm_add: the grouped form takes no gate and leaves no statistics; the runs are equal")
+        kernel("elementwise", "gg_group_rmsnorm_add")(_p(x), _p(y), _p(weight), x.numel() // H, H, int(groups), float(eps),
+                                                       int(zero_y), _stream())
+        return
     if (xhat is None) != (ssq is None):
         raise KernelError("rmsnorm_add: xhat and ssq come together")
     if xhat is not None:
@@ -187,6 +201,87 @@ def short_conv(h: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: 
     kernel("elementwise", "gg_short_conv")(_p(h), _p(out), dtype_code(h.dtype), _p(weight), _p(state), _p(cu_seqlens),
                                             _p(slots), _p(seq_of_token), int(n_tokens), int(n_seqs), W, taps, float(keep),
                                             int(max_new), _stream())
+
+
+def token_shift(x: torch.Tensor, out: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor,
+                slots: torch.Tensor, seq_of_token: torch.Tensor, n_tokens: int, n_seqs: int, max_new: int = 0) -> None:
+    """out[t] = x[t] + (x[t - 1] - x[t]) * mu inside each sequence (x float32, out the compute dtype); the row before
+    a sequence's first row of the step is state[slot] (float32 [slots, W]), which is then moved on to the step's last
+    row.  max_new: the most tokens one sequence brings, where the caller knows it (1: a single launch does both)."""
+    _need(x, torch.float32, "x")
+    _need(mu, torch.float32, "mu")
+    _need(state, torch.float32, "state")
+    W = x.shape[-1]
+    if mu.numel() != W or state.shape[-1] != W or not out.is_contiguous() or out.shape[-1] != W:
+        raise KernelError("token_shift: shapes disagree")
+    kernel("elementwise", "gg_token_shift")(_p(x), _p(out), dtype_code(out.dtype), _p(mu), _p(state), _p(cu_seqlens),
+                                             _p(slots), _p(seq_of_token), int(n_tokens), int(n_seqs), W, int(max_new),
+                                             _stream())
+
+
+def depth_mix(hist: torch.Tensor, x: torch.Tensor, coeff: Optional[torch.Tensor], store_at: int, n_terms: int) -> None:
+    """hist[store_at] = x; then, with n_terms > 0, x = sum_{j < n_terms} coeff[j] * hist[j] (all float32; hist is
+    [depth, *x.shape])."""
+    _need(hist, torch.float32, "hist")
+    _need(x, torch.float32, "x")
+    n = x.numel()
+    if hist.numel() < (max(store_at, n_terms - 1) + 1) * n:
+        raise KernelError("depth_mix: the history is too small")
+    if n_terms > 0:
+        _need(coeff, torch.float32, "coeff")
+        if coeff.numel() < n_terms:
+            raise KernelError("depth_mix: a coefficient per term")
+    kernel("elementwise", "gg_depth_mix")(_p(hist), _p(x), _p(coeff), int(store_at), int(n_terms), n, _stream())
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32) in the dtype of out."""
+    _need(x, torch.float32, "x")
+    if out.numel() != x.numel() or not out.is_contiguous():
+        raise KernelError("cast_rows: shapes disagree")
+    kernel("elementwise", "gg_cast_rows")(_p(x), _p(out), dtype_code(out.dtype), x.numel(), _stream())
+
+
+def gelu(z: torch.Tensor, out: torch.Tensor, tanh_form: bool = False) -> None:
+    """out = gelu(z), the exact (erf) form or the tanh form; float32 arithmetic; out may be z."""
+    if z.dtype != out.dtype or z.numel() != out.numel() or not z.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gelu: input and output must be contiguous and alike")
+    kernel("elementwise", "gg_gelu")(_p(z), _p(out), dtype_code(z.dtype), int(tanh_form), z.numel(), _stream())
+
+
+def row_gate(act: torch.Tensor, h: torch.Tensor, g: torch.Tensor, seq_of_token: Optional[torch.Tensor], n_tokens: int) -> None:
+    """act[t] *= sigmoid(g . h[t]) for every token: one gate per row from the row's input h and a stored vector g."""
+    _need(g, torch.float32, "gate vector")
+    if act.dtype != h.dtype or not act.is_contiguous() or not h.is_contiguous() or g.numel() != h.shape[-1]:
+        raise KernelError("row_gate: shapes disagree")
+    kernel("elementwise", "gg_row_gate")(_p(act), act.shape[-1], _p(h), h.shape[-1], dtype_code(act.dtype), _p(g),
+                                          _p(seq_of_token), int(n_tokens), _stream())
+
+
+def column_conv(h: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                in_bias: Optional[torch.Tensor], state: Optional[torch.Tensor], cu_seqlens: torch.Tensor,
+                slots: torch.Tensor, seq_of_token: torch.Tensor, n_tokens: int, n_seqs: int, act: int = 0,
+                max_new: int = 0) -> None:
+    """out[t] = act(bias + sum_j weight[j] * v[t - taps + 1 + j]) per channel inside each sequence, v = h + in_bias;
+    h [T, C] may be a column range of a wider buffer (compute dtype), out [T, C] is float32 (likewise), weight is
+    [taps, C] float32; rows before the step come from state [slots, taps - 1, C] (float32), which is then moved on.
+    act 0 none, 1 silu."""
+    taps, C = weight.shape
+    _need(weight, torch.float32, "taps")
+    if out.dtype != torch.float32 or h.stride(-1) != 1 or out.stride(-1) != 1 or h.shape[-1] != C or out.shape[-1] != C:
+        raise KernelError("column_conv: h [T, C] and out [T, C] (float32) have unit column stride")
+    for t in (bias, in_bias):
+        if t is not None:
+            _need(t, torch.float32, "bias")
+            if t.numel() != C:
+                raise KernelError("column_conv: a bias per channel")
+    if taps > 1:
+        _need(state, torch.float32, "state")
+        if tuple(state.shape[1:]) != (taps - 1, C):
+            raise KernelError("column_conv: the state is [slots, taps - 1, C]")
+    kernel("elementwise", "gg_column_conv")(_p(h), h.stride(0), dtype_code(h.dtype), _p(out), out.stride(0), _p(weight),
+                                             _p(bias), _p(in_bias), _p(state), _p(cu_seqlens), _p(slots), _p(seq_of_token),
+                                             int(n_tokens), int(n_seqs), C, taps, int(act), int(max_new), _stream())
 
 
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows: int) -> None:
@@ -276,6 +371,50 @@ def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         _p(q), _p(k_pool), _p(v_pool), _p(out), dtype_code(q.dtype), _p(positions), _p(seq_of_token),
         _p(page_table), page_table.shape[-1], page_size, k_pool.shape[0], n_tokens, nq, nkv, d, dv, float(scale),
         int(window), _p(sink), float(out_scale), _p(status_word(q.device)), _stream())
+
+
+def diff_qk_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: torch.Tensor, k_weight: Optional[torch.Tensor],
+                 eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                 seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int, k_pool: Optional[torch.Tensor],
+                 v_pool: Optional[torch.Tensor], n_tokens: int, heads: int, kv_heads: int, d: int, dv: int, rot: int) -> None:
+    """Preparation for differential attention: qkv [T, heads*2*d (+ kv_heads*2*d + kv_heads*dv with pools)]; every
+    (head, map) run of d is normed with a shared weight [d] and its first `rot` elements turned in adjacent pairs; q
+    to q_out [T, heads, 2, d], k into k_pool [page][kv_head][page_size][2 d], v into v_pool [..][dv]."""
+    if q_out.dtype != qkv.dtype or (k_pool is not None and (k_pool.dtype != qkv.dtype or v_pool.dtype != qkv.dtype)):
+        raise KernelError("diff_qk_prep: qkv, q_out and the cache must share one dtype")
+    want = heads * 2 * d + (kv_heads * (2 * d + dv) if k_pool is not None else 0)
+    if qkv.stride(-1) != 1 or qkv.shape[-1] != want or not q_out.is_contiguous():
+        raise KernelError("diff_qk_prep: the projection row's width does not fit the heads")
+    _need(q_weight, torch.float32, "q norm weight")
+    if k_pool is not None:
+        _need(k_weight, torch.float32, "k norm weight")
+        if k_pool.shape[-1] != 2 * d or v_pool.shape[-1] != dv or k_pool.shape[1] != kv_heads:
+            raise KernelError("diff_qk_prep: the pools do not fit the heads")
+    from .tcgen05_gemm import status_word
+    kernel("diff_attention", "gg_diff_qk_prep")(
+        _p(qkv), qkv.stride(0), dtype_code(qkv.dtype), _p(q_out), _p(q_weight), _p(k_weight), float(eps), _p(cos), _p(sin),
+        _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], int(page_size),
+        k_pool.shape[0] if k_pool is not None else 0, _p(k_pool), _p(v_pool), int(n_tokens), int(heads), int(kv_heads),
+        int(d), int(dv), int(rot), _p(status_word(qkv.device)), _stream())
+
+
+def diff_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                   seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int, n_tokens: int, heads: int,
+                   kv_heads: int, d: int, dv: int, scale: float, cap: float, window: int, lam: float, eps: float,
+                   out_scale: float) -> None:
+    """out[t, h] = out_scale * unit(a1 - lam * a2): two softmax attentions per head over the paged cache (keys
+    [page][kv_head][page_size][2 d], both maps side by side; values [..][dv]), scores bounded by cap tanh(s / cap)
+    where cap > 0, the difference divided by its root mean square (eps inside)."""
+    if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
+        raise KernelError("diff_attention: q, cache and out must share one dtype")
+    if k_pool.shape[-1] != 2 * d or v_pool.shape[-1] != dv or k_pool.shape[1] != kv_heads:
+        raise KernelError("diff_attention: the pools do not fit the heads")
+    from .tcgen05_gemm import status_word
+    kernel("diff_attention", "gg_diff_attention")(
+        _p(q), _p(k_pool), _p(v_pool), _p(out), dtype_code(q.dtype), _p(positions), _p(seq_of_token), _p(page_table),
+        page_table.shape[-1], int(page_size), k_pool.shape[0], int(n_tokens), int(heads), int(kv_heads), int(d), int(dv),
+        float(scale), float(cap), int(window), float(lam), float(eps), float(out_scale), _p(status_word(q.device)),
+        _stream())
 
 
 # ------------------------------------------------------------------------------- latent attention
@@ -476,6 +615,76 @@ def scan_finish(raw: torch.Tensor, x: Optional[torch.Tensor], g_off: int, out: t
         _p(seq_of_token), int(n_tokens), int(heads), int(dv), float(eps), float(out_scale), int(whole), int(gate), _stream())
 
 
+def stepsize_scan(xc: torch.Tensor, b_off: int, c_off: int, xd: torch.Tensor, dt_off: int, raw: torch.Tensor,
+                  state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor,
+                  dt_bias: torch.Tensor, neg_a: torch.Tensor, n_tokens: int, n_seqs: int, heads: int, groups: int, d: int,
+                  dv: int) -> None:
+    """S_t = g_t S_(t-1) + (dt B_t) v_t^T, o_t = S_t^T C_t per head with dt = softplus(x_dt + dt_bias), g = exp(neg_a
+    dt), from and into state [slots, heads, d, dv] (float32); raw [T, heads * dv] (float32) gets o_t.  xc [T, .]
+    float32 holds v heads at column 0, B [groups, d] at b_off, C at c_off; xd [T, .] (compute dtype) x_dt at dt_off."""
+    _need(raw, torch.float32, "raw")
+    _need(state, torch.float32, "state")
+    _need(dt_bias, torch.float32, "dt_bias")
+    _need(neg_a, torch.float32, "neg_a")
+    if xc.dtype != torch.float32 or xc.stride(-1) != 1 or xd.stride(-1) != 1:
+        raise KernelError("stepsize_scan: xc is float32 and rows are contiguous")
+    if tuple(state.shape[1:]) != (heads, d, dv) or raw.shape[-1] != heads * dv or dt_bias.numel() != heads or neg_a.numel() != heads:
+        raise KernelError("stepsize_scan: the state must be [slots, heads, d, dv], raw [T, heads * dv], constants [heads]")
+    kernel("recurrence", "gg_stepsize_scan")(
+        _p(xc), xc.stride(0), int(b_off), int(c_off), _p(xd), dtype_code(xd.dtype), xd.stride(0), int(dt_off), _p(raw),
+        _p(state), _p(cu_seqlens), _p(slots), _p(seq_of_token), _p(dt_bias), _p(neg_a), int(n_tokens), int(n_seqs),
+        int(heads), int(groups), int(d), int(dv), _stream())
+
+
+def stepsize_finish(raw: torch.Tensor, xc: torch.Tensor, xd: torch.Tensor, z_off: int, skip: torch.Tensor,
+                    weight: torch.Tensor, out: torch.Tensor, seq_of_token: torch.Tensor, n_tokens: int, heads: int, dv: int,
+                    norm_groups: int, eps: float) -> None:
+    """out[t] = groupnorm((raw[t] + skip_h * v[t]) * silu(z[t])) * weight in the dtype of out: v the heads' inputs
+    (xc columns 0.., float32), z the gate columns of xd at z_off; the norm in `norm_groups` equal runs."""
+    _need(raw, torch.float32, "raw")
+    _need(skip, torch.float32, "skip")
+    _need(weight, torch.float32, "norm weight")
+    if xd.dtype != out.dtype or not out.is_contiguous() or out.shape[-1] != heads * dv or weight.numel() != heads * dv:
+        raise KernelError("stepsize_finish: shapes disagree")
+    kernel("recurrence", "gg_stepsize_finish")(
+        _p(raw), _p(xc), xc.stride(0), _p(xd), dtype_code(xd.dtype), xd.stride(0), int(z_off), _p(skip), _p(weight), _p(out),
+        _p(seq_of_token), int(n_tokens), int(heads), int(dv), int(norm_groups), float(eps), _stream())
+
+
+# ------------------------------------------------------------------------------- vector-state recurrences
+def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor,
+                c: torch.Tensor, a: torch.Tensor, b: torch.Tensor, seq_of_token: torch.Tensor, n_tokens: int) -> None:
+    """a = exp(c * sigmoid(Wa u + ba)), b = sqrt(1 - a^2) * sigmoid(Wi u + bi) * u with block-diagonal Wa, Wi given
+    transposed as [blocks, in, out]; everything float32, u, a, b [T, C]."""
+    for t, n in ((u, "u"), (wa_t, "wa"), (wi_t, "wi"), (ba, "ba"), (bi, "bi"), (c, "c"), (a, "a"), (b, "b")):
+        _need(t, torch.float32, n)
+    blocks, bw, _ = wa_t.shape
+    C = blocks * bw
+    if u.shape[-1] != C or a.shape[-1] != C or b.shape[-1] != C or wi_t.shape != wa_t.shape or c.numel() != C:
+        raise KernelError("rglru_gates: shapes disagree")
+    kernel("diag_recurrence", "gg_rglru_gates")(_p(u), _p(wa_t), _p(wi_t), _p(ba), _p(bi), _p(c), _p(a), _p(b),
+                                                 _p(seq_of_token), int(n_tokens), C, blocks, _stream())
+
+
+def diag_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, ybias: Optional[torch.Tensor], out: torch.Tensor,
+              state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor,
+              n_tokens: int, n_seqs: int) -> None:
+    """S_t = a_t S_(t-1) + b_t per channel from and into state [slots, C] (float32); out[t] = S_t * gelu_tanh(y[t] +
+    ybias) in the compute dtype (y [T, C] may be a column range of a wider buffer of that dtype)."""
+    _need(a, torch.float32, "a")
+    _need(b, torch.float32, "b")
+    _need(state, torch.float32, "state")
+    C = a.shape[-1]
+    if y.dtype != out.dtype or y.stride(-1) != 1 or y.shape[-1] != C or not out.is_contiguous() or out.shape[-1] != C \
+            or state.shape[-1] != C:
+        raise KernelError("diag_scan: shapes disagree")
+    if ybias is not None:
+        _need(ybias, torch.float32, "ybias")
+    kernel("diag_recurrence", "gg_diag_scan")(_p(a), _p(b), _p(y), y.stride(0), dtype_code(y.dtype), _p(ybias), _p(out),
+                                               _p(state), _p(cu_seqlens), _p(slots), _p(seq_of_token), int(n_tokens),
+                                               int(n_seqs), C, _stream())
+
+
 # ------------------------------------------------------------------------------- routed experts
 def moe_router_logits(h: torch.Tensor, wr: torch.Tensor, z: torch.Tensor, n_tokens: int) -> None:
     """z[t, e] = wr[e] . h[t], float32 sums on the CUDA cores (the router is never computed in reduced precision)."""
@@ -489,10 +698,12 @@ def moe_router_logits(h: torch.Tensor, wr: torch.Tensor, z: torch.Tensor, n_toke
 
 def moe_route(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, seq_of_token: Optional[torch.Tensor],
               softmax: bool = False, renormalize: bool = False, rows: Optional[int] = None,
-              correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1) -> None:
+              correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1, n_real: int = 0,
+              scale: float = 1.0) -> None:
     """The `top` experts of every row of z and their weights.  correction (float32 [E], optional) is added to the
     scores for the choice only; with groups > 1 the experts form that many equal runs of neighbours and only the
-    `keep` groups whose two best choice scores sum highest can be chosen from."""
+    `keep` groups whose two best choice scores sum highest can be chosen from.  n_real (0: all): router outputs
+    from n_real on stand for no expert, a choice of one is stored as index -1; scale multiplies the weights."""
     _need(z, torch.float32, "router logits")
     if correction is not None:
         _need(correction, torch.float32, "correction")
@@ -500,7 +711,8 @@ def moe_route(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, s
     _need(wts, torch.float32, "wts")
     T = z.shape[0] if rows is None else rows
     kernel("moe", "gg_moe_route")(_p(z), T, z.shape[-1], int(top), int(softmax), int(renormalize), _p(correction),
-                                   int(groups), int(keep), _p(idx), _p(wts), _p(seq_of_token), _stream())
+                                   int(groups), int(keep), int(n_real), float(scale), _p(idx), _p(wts), _p(seq_of_token),
+                                   _stream())
 
 
 def moe_gate_up(h: torch.Tensor, w_gu: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, y: torch.Tensor,
@@ -536,12 +748,25 @@ def moe_gather(h: torch.Tensor, wts: torch.Tensor, place: Optional[torch.Tensor]
 
 
 def moe_combine(rows: torch.Tensor, place: Optional[torch.Tensor], residual: torch.Tensor, n_tokens: int, top: int,
-                seq_of_token: Optional[torch.Tensor]) -> None:
-    """residual[t] += sum over k (in order) of rows[place[t * top + k]], or of rows[t * top + k] without `place`."""
+                seq_of_token: Optional[torch.Tensor], idx: Optional[torch.Tensor] = None) -> None:
+    """residual[t] += sum over k (in order) of rows[place[t * top + k]], or of rows[t * top + k] without `place`;
+    with `idx`, pairs whose index is negative (a choice without an expert) are left out."""
     _need(rows, torch.float32, "rows")
     _need(residual, torch.float32, "residual")
     kernel("moe", "gg_moe_combine")(_p(rows), _p(place), _p(residual), int(n_tokens), residual.shape[-1], int(top),
-                                     _p(seq_of_token), _stream())
+                                     _p(seq_of_token), _p(idx), _stream())
+
+
+def moe_identity(h: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, residual: torch.Tensor, n_tokens: int, top: int,
+                 seq_of_token: Optional[torch.Tensor]) -> None:
+    """residual[t] += (sum of wts[t, k] over the choices with idx[t, k] < 0) * h[t]: the identity experts."""
+    _need(residual, torch.float32, "residual")
+    _need(idx, torch.int32, "idx")
+    _need(wts, torch.float32, "wts")
+    if not h.is_contiguous() or h.shape[-1] != residual.shape[-1]:
+        raise KernelError("moe_identity: shapes disagree")
+    kernel("moe", "gg_moe_identity")(_p(h), dtype_code(h.dtype), _p(idx), _p(wts), _p(residual), int(n_tokens),
+                                      residual.shape[-1], int(top), _p(seq_of_token), _stream())
 
 
 MOE_MMA_MAX_PAIRS = 8192      # the most (token, choice) pairs the mma.sync experts kernel takes (csrc/moe.cu)

@@ -54,6 +54,7 @@ GG_API gg_moe_router_logits(const void* h, int h_dtype, const void* wr, int w_dt
 // ----------------------------------------------------------------------------- route
 // One warp per token.  z [T, E] float32 logits.  softmax != 0: scores are softmax(z), else sigmoid(z).
 __global__ void __launch_bounds__(32) moe_route_kernel(const float* z, int E, int top, int softmax, int renorm,
+                                                       int n_real, float scale,
                                                        int* idx, float* wts, const int* __restrict__ seq_of_token) {
     pdl_launch();
     pdl_wait();
@@ -90,14 +91,15 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const float* z, int E, in
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
         const float s = softmax ? expf(bv - mx) / den : 1.0f / (1.0f + expf(-bv));
-        if (lane == 0) { idx[(size_t)t * top + k] = bi; wts[(size_t)t * top + k] = s; }
+        if (lane == 0) { idx[(size_t)t * top + k] = bi < n_real ? bi : -1; wts[(size_t)t * top + k] = s; }
         total += s;
         prev_v = bv;
         prev_i = bi;
     }
-    if (renorm) {
+    if (renorm || scale != 1.0f) {
         __syncwarp();
-        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] /= total;
+        const float f = renorm ? scale / (total + 1e-20f) : scale;
+        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= f;
     }
 }
 
@@ -108,6 +110,7 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const float* z, int E, in
 // the chosen experts' scores s without the correction.  One warp per token; scores in shared memory.
 __global__ void __launch_bounds__(32) moe_route_grouped_kernel(const float* z, int E, int top, int softmax, int renorm,
                                                                const float* __restrict__ correction, int groups, int keep,
+                                                               int n_real, float scale,
                                                                int* idx, float* wts, const int* __restrict__ seq_of_token) {
     pdl_launch();
     pdl_wait();
@@ -182,31 +185,40 @@ __global__ void __launch_bounds__(32) moe_route_grouped_kernel(const float* z, i
         }
         if (bi >= E) bi = 0;                                  // fewer candidates than `top` (refused by the launcher)
         const float s = sc[bi];
-        if (lane == 0) { idx[(size_t)t * top + k] = bi; wts[(size_t)t * top + k] = bv == -INFINITY ? 0.f : s; ch[bi] = -INFINITY; }
+        if (lane == 0) {
+            idx[(size_t)t * top + k] = bi < n_real ? bi : -1;
+            wts[(size_t)t * top + k] = bv == -INFINITY ? 0.f : s;
+            ch[bi] = -INFINITY;
+        }
         total += s;
         __syncwarp();
     }
-    if (renorm) {
-        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] /= total;
+    if (renorm || scale != 1.0f) {
+        const float f = renorm ? scale / (total + 1e-20f) : scale;
+        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= f;
     }
 }
 
 // correction [E] (may be null); groups >= 1 equal runs of neighbouring experts of which `keep` can be chosen from.
+// n_real (0: all E): router outputs from n_real on have no expert behind them (identity experts: the caller adds
+// weight times the token's own row); a choice of one is stored as index -1 with its weight.  scale multiplies the
+// weights after the renormalisation (which divides by the chosen scores' sum + 1e-20).
 GG_API gg_moe_route(const float* z, int T, int E, int top, int softmax, int renorm, const float* correction, int groups,
-                    int keep, int* idx, float* wts, const int* seq_of_token, cudaStream_t stream) {
+                    int keep, int n_real, float scale, int* idx, float* wts, const int* seq_of_token, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E) return GG_ERR_ARG;
+    if (E <= 0 || top <= 0 || top > E || n_real < 0 || n_real > E) return GG_ERR_ARG;
+    if (n_real == 0) n_real = E;
     if (groups < 1) groups = 1;
     if (keep < 1 || keep > groups) keep = groups;
     if (correction == nullptr && keep == groups) {
-        gg_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, 1, z, E, top, softmax, renorm, idx, wts, seq_of_token);
+        gg_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, 1, z, E, top, softmax, renorm, n_real, scale, idx, wts, seq_of_token);
         return gg_last_error();
     }
     if (E % groups || top > (E / groups) * keep) return GG_ERR_ARG;
     const size_t smem = ((size_t)2 * E + groups) * sizeof(float);
     if (smem > 48 * 1024) return GG_ERR_ARG;
     gg_launch(moe_route_grouped_kernel, dim3(T), dim3(32), smem, stream, 1, z, E, top, softmax, renorm, correction, groups,
-              keep, idx, wts, seq_of_token);
+              keep, n_real, scale, idx, wts, seq_of_token);
     return gg_last_error();
 }
 
@@ -229,6 +241,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const TX* h, const TW*
     extern __shared__ float xs[];
     const int p = blockIdx.x, t = p / top;
     const int e = idx[p];
+    if (e < 0) return;                                   // a choice without an expert: nothing reads its row
     const float wt = wts[p];
     const float xin = weight_on_input ? wt : 1.0f;
     const TX* ht = h + (size_t)t * W;
@@ -293,6 +306,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const TY* y, const TW* __
         __syncthreads();
         if (n < W) {
             const int e = idx[(size_t)t * top + k];
+            if (e < 0) continue;                         // a choice without an expert
             const TW* wr = w_d + ((size_t)e * W + n) * F;
             float s = 0.f;
             for (int i = lane; i < F; i += 32) s = fmaf(to_f<TW>(wr[i]), ys[i], s);
@@ -410,7 +424,7 @@ GG_API gg_moe_invert(const int* place, int* pair_of, int P, cudaStream_t stream)
 
 // residual[t, :] += sum_k rows[place[t * top + k], :]  (without `place`: the rows are in pair order)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* rows, const int* place, float* residual, int W,
-                                                          int top, const int* __restrict__ seq_of_token) {
+                                                          int top, const int* __restrict__ seq_of_token, const int* idx) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
@@ -419,16 +433,45 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* rows, con
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
             const size_t p = (size_t)t * top + k;
+            if (idx != nullptr && idx[p] < 0) continue;      // a choice without an expert left no row
             s += rows[(place != nullptr ? (size_t)place[p] : p) * W + i];
         }
         residual[(size_t)t * W + i] += s;
     }
 }
 
+// idx (may be null): the pairs' expert indices; pairs whose index is negative are left out.
 GG_API gg_moe_combine(const float* rows, const int* place, float* residual, int T, int W, int top,
-                      const int* seq_of_token, cudaStream_t stream) {
+                      const int* seq_of_token, const int* idx, cudaStream_t stream) {
     if (T <= 0) return 0;
-    gg_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, 1, rows, place, residual, W, top, seq_of_token);
+    gg_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, 1, rows, place, residual, W, top, seq_of_token, idx);
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- identity experts
+// residual[t, :] += sum over the choices k of token t whose index is negative of wts[t, k] * h[t, :]: an identity
+// expert gives back its input, times the router's weight.  One block per token.
+template <typename TX>
+__global__ void __launch_bounds__(256) moe_identity_kernel(const TX* h, const int* idx, const float* wts, float* residual,
+                                                           int W, int top, const int* __restrict__ seq_of_token) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (seq_of_token != nullptr && seq_of_token[t] < 0) return;
+    float f = 0.f;
+    for (int k = 0; k < top; ++k)
+        if (idx[(size_t)t * top + k] < 0) f += wts[(size_t)t * top + k];
+    if (f == 0.f) return;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) residual[(size_t)t * W + i] += f * to_f<TX>(h[(size_t)t * W + i]);
+}
+
+GG_API gg_moe_identity(const void* h, int h_dtype, const int* idx, const float* wts, float* residual, int T, int W, int top,
+                       const int* seq_of_token, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (W <= 0 || top <= 0) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(h_dtype, TX,
+        gg_launch(moe_identity_kernel<TX>, dim3(T), dim3(256), 0, stream, 1, (const TX*)h, idx, wts, residual, W, top,
+                  seq_of_token));
     return gg_last_error();
 }
 

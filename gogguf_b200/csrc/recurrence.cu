@@ -656,3 +656,185 @@ GG_API gg_gated_scan_chunks(const void* x, int dtype, long long ld, int q_off, i
 #undef GG_CHUNKS
     return gg_last_error();
 }
+
+// ----------------------------------------------------------------------------- a step size per head (state-space form)
+// The same matrix state with a gate that is one number per head and token, made from a step size:
+//     dt = softplus(x_dt + dt_bias_h),   g_t = exp(neg_a_h * dt)   (neg_a_h = -exp(A_log_h) <= 0, made by the caller)
+//     S_t = g_t S_(t-1) + (dt B_t) v_t^T,   o_t = S_t^T C_t
+// S [d][dv] with d the state size and dv the head's value size.  B and C [groups][d] are shared by the heads of a
+// group (head h reads group h / (H / groups)).  v, B and C arrive as float32 columns of one row per token
+// (xc [T, ldc]: v heads at column 0, B at b_off, C at c_off: a convolution's output); x_dt as column dt_off + h of
+// the projection's row in the compute dtype (xd [T, ldd]).  The structure is gated_scan_kernel's: grid (sequence,
+// head, tile of 32 columns), thread (part, j) owns RPT rows of column j of the state, rounds of REC_TB tokens.
+__device__ __forceinline__ float rec_softplus(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.f); }
+
+template <typename T, int RPT>
+__global__ void __launch_bounds__(256) stepsize_scan_kernel(
+    const float* xc, long long ldc, int b_off, int c_off, const T* xd, long long ldd, int dt_off, float* raw, float* state,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ seq_of_token,
+    const float* __restrict__ dt_bias, const float* __restrict__ neg_a, int H, int d, int dv, int parts, int hpg) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * REC_COLS;
+    const int ncols = min(REC_COLS, dv - j0);
+    const int dp = parts * RPT;
+    float* qs = sm;                             // [REC_TB][dp]  C_t
+    float* ks = qs + REC_TB * dp;               // [REC_TB][dp]  dt B_t
+    float* vs = ks + REC_TB * dp;               // [REC_TB][REC_COLS]
+    float* os = vs + REC_TB * REC_COLS;         // [REC_TB][parts][REC_COLS]
+    float* dts = os + REC_TB * parts * REC_COLS;  // [REC_TB] dt
+    float* gs = dts + REC_TB;                   // [REC_TB] g
+    const int start = cu_seqlens[b], end = cu_seqlens[b + 1];
+    if (end <= start) return;
+    const size_t HV = (size_t)H * dv;
+    if (seq_of_token[start] < 0) {
+        for (int t = start; t < end; ++t)
+            for (int j = threadIdx.x; j < ncols; j += blockDim.x) raw[(size_t)t * HV + h * dv + j0 + j] = 0.f;
+        return;
+    }
+    const int part = threadIdx.x / REC_COLS, j = threadIdx.x - part * REC_COLS;
+    const bool live = j < ncols;
+    const int r0 = part * RPT;
+    const int grp = h / hpg;
+    const float bias = dt_bias[h], na = neg_a[h];
+    float* sp = state + (((size_t)slots[b] * H + h) * d) * dv + j0 + j;
+    float S[RPT];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) S[i] = (live && r0 + i < d) ? sp[(size_t)(r0 + i) * dv] : 0.f;
+    if (dp > d)
+        for (int idx = threadIdx.x; idx < REC_TB * (dp - d); idx += blockDim.x) {
+            const int tt = idx / (dp - d), i = d + idx % (dp - d);
+            qs[tt * dp + i] = 0.f;
+            ks[tt * dp + i] = 0.f;
+        }
+    for (int t0 = start; t0 < end; t0 += REC_TB) {
+        const int nb = min(REC_TB, end - t0);
+        if (threadIdx.x < nb) {
+            const float dt = rec_softplus(to_f<T>(xd[(size_t)(t0 + threadIdx.x) * ldd + dt_off + h]) + bias);
+            dts[threadIdx.x] = dt;
+            gs[threadIdx.x] = expf(na * dt);
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nb * d; idx += blockDim.x) {
+            const int tt = idx / d, i = idx - tt * d;
+            const float* row = xc + (size_t)(t0 + tt) * ldc;
+            qs[tt * dp + i] = row[c_off + grp * d + i];
+            ks[tt * dp + i] = dts[tt] * row[b_off + grp * d + i];
+        }
+        for (int idx = threadIdx.x; idx < nb * ncols; idx += blockDim.x) {
+            const int tt = idx / ncols, c = idx - tt * ncols;
+            vs[tt * REC_COLS + c] = xc[(size_t)(t0 + tt) * ldc + h * dv + j0 + c];
+        }
+        __syncthreads();
+        if (live) {
+#pragma unroll 1
+            for (int tt = 0; tt < nb; ++tt) {
+                const float vj = vs[tt * REC_COLS + j], g = gs[tt];
+                const float* kt = ks + tt * dp + r0;
+                const float* qt = qs + tt * dp + r0;
+                float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < RPT; i += 2) {
+                    S[i] = fmaf(g, S[i], kt[i] * vj);
+                    S[i + 1] = fmaf(g, S[i + 1], kt[i + 1] * vj);
+                    o0 = fmaf(S[i], qt[i], o0);
+                    o1 = fmaf(S[i + 1], qt[i + 1], o1);
+                }
+                os[(tt * parts + part) * REC_COLS + j] = o0 + o1;
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nb * ncols; idx += blockDim.x) {
+            const int tt = idx / ncols, c = idx - tt * ncols;
+            float o = 0.f;
+            for (int p = 0; p < parts; ++p) o += os[(tt * parts + p) * REC_COLS + c];
+            raw[(size_t)(t0 + tt) * HV + h * dv + j0 + c] = o;
+        }
+        // (the next round writes dts / gs before its first barrier: every thread has read gs in the loop above, which
+        // ends before the barrier that precedes these stores)
+    }
+#pragma unroll
+    for (int i = 0; i < RPT; ++i)
+        if (live && r0 + i < d) sp[(size_t)(r0 + i) * dv] = S[i];
+}
+
+// xc [T, ldc] float32; xd [T, ldd] in `dtype`; raw [T, H dv] float32; state [slots][H][d][dv] float32;
+// dt_bias, neg_a [H]; groups divides H.
+GG_API gg_stepsize_scan(const float* xc, long long ldc, int b_off, int c_off, const void* xd, int dtype, long long ldd,
+                        int dt_off, float* raw, float* state, const int* cu_seqlens, const int* slots,
+                        const int* seq_of_token, const float* dt_bias, const float* neg_a, int ntok, int n_seqs, int H,
+                        int groups, int d, int dv, cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (H <= 0 || H > 65535 || groups <= 0 || H % groups || d <= 0 || d > 256 || dv <= 0 || raw == nullptr ||
+        state == nullptr || dt_bias == nullptr || neg_a == nullptr)
+        return GG_ERR_ARG;
+    const int rpt = d <= 64 ? 16 : 32;
+    const int parts = (d + rpt - 1) / rpt;
+    const int tiles = (dv + REC_COLS - 1) / REC_COLS;
+    if (tiles > 65535) return GG_ERR_ARG;
+    const size_t smem = ((size_t)2 * REC_TB * parts * rpt + (size_t)REC_TB * REC_COLS * (1 + parts) + 2 * REC_TB) * sizeof(float);
+    if (smem > 200 * 1024) return GG_ERR_ARG;
+#define GG_SSCAN(T_, R_)                                                                                             \
+    do {                                                                                                             \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(stepsize_scan_kernel<T_, R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        gg_launch(stepsize_scan_kernel<T_, R_>, dim3(n_seqs, H, tiles), dim3(parts * REC_COLS), smem, stream, 1, xc, ldc, \
+                  b_off, c_off, (const T_*)xd, ldd, dt_off, raw, state, cu_seqlens, slots, seq_of_token, dt_bias, neg_a, \
+                  H, d, dv, parts, H / groups);                                                                      \
+    } while (0)
+    GG_DISPATCH_DTYPE(dtype, T, if (rpt == 16) GG_SSCAN(T, 16); else GG_SSCAN(T, 32));
+#undef GG_SSCAN
+    return gg_last_error();
+}
+
+// The finish of that form, one block per token: val = (raw + skip_h * v) * silu(z), with v the head's input row
+// (xc, float32) and z the gate's columns of the projection (xd, compute dtype); the row of H dv numbers is then cut
+// into `norm_groups` equal runs, each divided by its own sqrt(mean(run^2) + eps), times w [H dv]; stored in the
+// compute dtype.  The gate comes before the norm.
+template <typename T>
+__global__ void __launch_bounds__(256) stepsize_finish_kernel(const float* raw, const float* xc, long long ldc, const T* xd,
+                                                              long long ldd, int z_off, const float* __restrict__ skip,
+                                                              const float* __restrict__ w, T* out,
+                                                              const int* __restrict__ seq_of_token, int H, int dv,
+                                                              int norm_groups, float eps) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const int n = H * dv;
+    T* o = out + (size_t)t * n;
+    if (seq_of_token[t] < 0) {
+        for (int c = threadIdx.x; c < n; c += blockDim.x) o[c] = from_f<T>(0.f);
+        return;
+    }
+    const float* r = raw + (size_t)t * n;
+    const float* v = xc + (size_t)t * ldc;
+    const T* z = xd + (size_t)t * ldd + z_off;
+    const int gs = n / norm_groups;
+    auto val = [&](int c) {
+        const float zz = to_f<T>(z[c]);
+        return (r[c] + skip[c / dv] * v[c]) * (zz * rec_sigmoid(zz));
+    };
+    for (int g = 0; g < norm_groups; ++g) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float a = val(g * gs + i); ss = fmaf(a, a, ss); }
+        ss = block_sum(ss, red);
+        const float f = 1.0f / sqrtf(ss / (float)gs + eps);
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            const int c = g * gs + i;
+            o[c] = from_f<T>(val(c) * f * w[c]);
+        }
+    }
+}
+
+GG_API gg_stepsize_finish(const float* raw, const float* xc, long long ldc, const void* xd, int dtype, long long ldd,
+                          int z_off, const float* skip, const float* w, void* out, const int* seq_of_token, int ntok, int H,
+                          int dv, int norm_groups, float eps, cudaStream_t stream) {
+    if (ntok <= 0) return 0;
+    if (H <= 0 || dv <= 0 || norm_groups <= 0 || (H * dv) % norm_groups || skip == nullptr || w == nullptr) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(stepsize_finish_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, raw, xc, ldc, (const T*)xd, ldd, z_off, skip,
+                  w, (T*)out, seq_of_token, H, dv, norm_groups, eps));
+    return gg_last_error();
+}

@@ -30,10 +30,11 @@ def check_status(device: torch.device) -> None:
     v = int(t.item())
     if v != 0:
         t.zero_()
-        if 41 <= v <= 48:
+        if 41 <= v <= 51:
             who = {41: "attention_plain", 42: "attn_decode", 43: "attn_prefill", 44: "attn_decode_tma",
                    45: "attn_prefill_tc", 46: "qk_norm_rope_cache", 47: "qk_norm_rope_cache (16-byte form)",
-                   48: "the q/k/v product's cache write"}[v]
+                   48: "the q/k/v product's cache write", 49: "latent_prep", 50: "diff_qk_prep",
+                   51: "diff_attention"}[v]
             raise KernelError(f"debug build: kernel {who} met a page-table index or page id out of range (code {v}); "
                               "it read page 0 (a reader) or wrote nothing (a writer), results of that step are invalid")
         raise KernelError(f"a bounded wait inside a kernel ran out (code {v}: 1 TMA producer, 2 MMA issuer, "

@@ -38,7 +38,7 @@ def _part_class(table, spec: PartSpec, what: str):
 
 
 _FAMILIES = {"mixer": (R.MIXERS, "mixer"), "feed_forward": (R.FEED_FORWARDS, "feed-forward"),
-             "norm": (R.NORMS, "norm"), "gate": (R.GATES, "gate")}
+             "norm": (R.NORMS, "norm"), "gate": (R.GATES, "gate"), "stream": (R.STREAMS, "stream operation")}
 
 
 def _block_parts(b: BlockSpec) -> List[Tuple[str, PartSpec, type]]:

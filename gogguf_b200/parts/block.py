@@ -182,6 +182,55 @@ class SandwichNormBlock:
                        self.ff_folded, stats, emit=True, gate=self.ff_gate)
 
 
+@register_arrangement("post_norm")
+class PostNormBlock:
+    """A norm on a part's output only: x += post1(mixer(x)); x += post2(feed_forward(x)).  The parts read the stream
+    itself (rounded to the compute dtype; a mixer that declares ``reads_stream`` is handed the float32 rows).  A
+    part's output is collected in a zeroed float32 buffer; the norm after the part and the add into the stream are
+    one kernel, all in float32.  The norms expose `weight`, `eps` and, for a norm in groups, `groups`.  The
+    feed-forward (with its norm) may be absent.  A `stream` part (role stream_mix, optional) runs before and after
+    the block's parts on the stream as a whole."""
+
+    roles = {"mixer": "mixer", "mixer_post_norm": "norm", "feed_forward": "feed_forward",
+             "feed_forward_post_norm": "norm", "stream_mix": "stream"}
+    optional_roles = ("feed_forward", "feed_forward_post_norm", "stream_mix")
+    ZEROED = SandwichNormBlock.ZEROED
+
+    def __init__(self, spec: BlockSpec, parts: Dict[str, object], rt: Runtime):
+        self.parts = dict(parts)
+        self.rt = rt
+        self.mixer, self.mixer_post = parts["mixer"], parts["mixer_post_norm"]
+        self.feed_forward, self.ff_post = parts.get("feed_forward"), parts.get("feed_forward_post_norm")
+        self.stream = parts.get("stream_mix")
+        if (self.feed_forward is None) != (self.ff_post is None):
+            raise ValueError("post_norm: a feed-forward and feed_forward_post_norm come together")
+
+    def _rows(self, x: torch.Tensor, ctx: StepContext, direct: bool) -> torch.Tensor:
+        if direct or self.rt.dtype == torch.float32:
+            return x
+        h = ctx.ws.get("block_stream_rows", tuple(x.shape), self.rt.dtype)
+        K.cast_rows(x, h)
+        return h
+
+    def _part(self, x: torch.Tensor, ctx: StepContext, post, call, direct: bool) -> None:
+        y = ctx.ws.get("block_part_out", tuple(x.shape), torch.float32)
+        if ctx.shared.get(self.ZEROED) != y.data_ptr():
+            y.zero_()
+        call(self._rows(x, ctx, direct), y)
+        K.rmsnorm_add(x, y, post.weight, post.eps, zero_y=True, groups=int(getattr(post, "groups", 1)))
+        ctx.shared[self.ZEROED] = y.data_ptr()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache, writes_cache: bool) -> None:
+        if self.stream is not None:
+            self.stream.begin(x, ctx)
+        self._part(x, ctx, self.mixer_post, lambda h, y: self.mixer.forward(h, y, ctx, cache, writes_cache),
+                   bool(getattr(self.mixer, "reads_stream", False)))
+        if self.feed_forward is not None:
+            self._part(x, ctx, self.ff_post, lambda h, y: self.feed_forward.forward(h, y, ctx), False)
+        if self.stream is not None:
+            self.stream.finish(x, ctx)
+
+
 def _offer_norm(part, norm, rt: Runtime) -> bool:
     absorb = getattr(part, "absorb_norm", None)
     if absorb is None or not (rt.fast and rt.fold_norms and rt.dtype == torch.bfloat16):

@@ -10,8 +10,12 @@ weights stay the scores themselves; `groups` {count, keep}: the experts form `co
 group's score is the sum of its two largest choice scores, and only experts of the `keep` best groups can be chosen.  An expert is a gated unit: y = act(Wg x, Wu x), out = Wd y, with
 act "clamped_glu": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + up_offset)
 (up_offset 1 unless given); act "silu_glu": silu(g) u, the same unit without a limit, with slope 1 and offset 0.
-`shared` (optional: intermediate_size, prefix, names) adds one dense gated unit that every token runs
-(the `swiglu` feed-forward under the given prefix), summed with the routed experts' output.
+`shared` (optional: intermediate_size, prefix, names, row_gate) adds one dense gated unit that every token runs
+(the `swiglu` feed-forward under the given prefix), summed with the routed experts' output; with `row_gate` its
+output is multiplied by one sigmoid gate per token.  `identity` (a count, default 0): the router has that many
+outputs beyond `num_experts` with no matrices behind them; choosing one adds the token's own input row times the
+weight.  `weight_scale` multiplies the weights after the renormalisation (which divides by the chosen scores' sum
++ 1e-20).
 The experts' matrices are reached through the chosen index with nothing read back: on the CUDA cores pair by pair
 (the 32-bit path, sizes the tensor-core forms do not take), or in bfloat16 on mma.sync, a CTA per expert and 64
 output rows with the expert's pairs as the operand (decode steps, short prompts).  Steps of many tokens in
@@ -88,11 +92,12 @@ class RoutedExperts:
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
         h, i, E = spec["hidden_size"], spec["intermediate_size"], spec["num_experts"]
+        R = E + int(spec.get("identity", 0))          # router outputs
         n = cls._names(spec)
-        t = {n["router"]: TensorDecl(shape=(E, h))}
+        t = {n["router"]: TensorDecl(shape=(R, h))}
         if spec.get("correction"):
             # (a correction evens out the experts' load: small next to the scores' spread, or the choice is its alone)
-            t[n["correction"]] = TensorDecl(shape=(E,), init="zeros_normal")
+            t[n["correction"]] = TensorDecl(shape=(R,), init="zeros_normal")
         for e in range(E):
             p = n["expert"].format(e)
             t[p + n["gate"]] = TensorDecl(shape=(i, h))
@@ -113,12 +118,19 @@ class RoutedExperts:
         params = dict(hidden_size=spec["hidden_size"], intermediate_size=sh["intermediate_size"])
         if sh.get("names"):
             params["names"] = dict(sh["names"])
+        if sh.get("row_gate"):
+            params["row_gate"] = True
         return PartSpec(kind=sh.get("kind", "swiglu"), prefix=sh.get("prefix", "shared."), params=params)
 
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         self.rt = rt
         self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
         self.E, self.top = int(spec["num_experts"]), int(spec["top_k"])
+        self.identity = int(spec.get("identity", 0))
+        self.R = self.E + self.identity              # router outputs
+        self.weight_scale = float(spec.get("weight_scale", 1.0))
+        if self.identity < 0 or self.top > self.R:
+            raise ValueError(f"routed experts: top_k={self.top} of {self.R} router outputs")
         score = spec.get("score", "sigmoid")
         if score not in ("sigmoid", "softmax"):
             raise ValueError(f"routed experts: unknown score {score!r} (sigmoid, softmax)")
@@ -144,10 +156,10 @@ class RoutedExperts:
         gr = dict(spec.get("groups") or {})
         self.groups = int(gr.get("count", 1))
         self.keep = int(gr.get("keep", self.groups))
-        if self.groups < 1 or self.E % self.groups or not (1 <= self.keep <= self.groups):
-            raise ValueError(f"routed experts: {self.E} experts do not form {self.groups} equal groups of which "
+        if self.groups < 1 or self.R % self.groups or not (1 <= self.keep <= self.groups):
+            raise ValueError(f"routed experts: {self.R} experts do not form {self.groups} equal groups of which "
                              f"{self.keep} are kept")
-        if self.top > (self.E // self.groups) * self.keep:
+        if self.top > (self.R // self.groups) * self.keep:
             raise ValueError(f"routed experts: top_k={self.top} exceeds the experts of the {self.keep} kept groups")
         gu: List[torch.Tensor] = []
         dn: List[torch.Tensor] = []
@@ -172,7 +184,8 @@ class RoutedExperts:
         # rows on 16-byte boundaries: what the tensor-core forms (mma.sync for few pairs, tcgen05 for many) take
         self._mma = (rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16
                      and self.hidden % 8 == 0 and self.inter % 8 == 0)
-        if rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16:
+        # (the sorted form files every pair under its expert; pairs without one keep to the forms through the index)
+        if rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16 and not self.identity:
             from . import experts_grouped
             self._grouped = experts_grouped.try_make(self)
 
@@ -186,12 +199,13 @@ class RoutedExperts:
 
     def route(self, h: torch.Tensor, ctx: StepContext):
         T = ctx.n_tokens
-        z = ctx.ws.get("moe_logits", (T, self.E), torch.float32)
+        z = ctx.ws.get("moe_logits", (T, self.R), torch.float32)
         K.moe_router_logits(h, self.router_w, z, T)      # CUDA cores, float32 sums: the router is never reduced
         idx = ctx.ws.get("moe_idx", (T, self.top), torch.int32)
         wts = ctx.ws.get("moe_wts", (T, self.top), torch.float32)
         K.moe_route(z, self.top, idx, wts, ctx.seq_of_token, softmax=self.softmax, renormalize=self.renorm, rows=T,
-                    correction=self.correction, groups=self.groups, keep=self.keep)
+                    correction=self.correction, groups=self.groups, keep=self.keep,
+                    n_real=self.E if self.identity else 0, scale=self.weight_scale)
         return idx, wts
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
@@ -202,6 +216,10 @@ class RoutedExperts:
     def _routed(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         T = ctx.n_tokens
         idx, wts = self.route(h, ctx)
+        if self.identity:
+            if self.on_input:
+                raise ValueError("routed experts: identity experts take their weight on the output")
+            K.moe_identity(h, idx, wts, residual, T, self.top, ctx.seq_of_token)
         P = T * self.top
         # the sorted form pays one launch per expert and matrix behind a read-back: worth it where an expert's
         # product is large (measured: 256 rows of 2,048 x 4,096 yes, of 1,024 x 2,048 no)
@@ -210,16 +228,20 @@ class RoutedExperts:
         if self._grouped is not None and self._grouped.takes(ctx) and not prefer_mma:
             self._grouped.run(h, idx, wts, residual, ctx)
             return
-        if self._mma and P <= K.MOE_MMA_MAX_PAIRS and h.dtype == torch.bfloat16:
+        if self._mma and h.dtype == torch.bfloat16 and (P <= K.MOE_MMA_MAX_PAIRS or self._grouped is None):
             # few pairs in bfloat16: the experts' rows stream once through mma.sync, the pairs' rows as the operand
+            # (more pairs than one launch takes, where the sorted form does not serve: a launch per slice of pairs)
             xs = ctx.ws.get("moe_rows_in", (P, self.hidden), torch.bfloat16)
             K.moe_gather(h, wts, None, xs, P, self.top, self.on_input)
             yb = ctx.ws.get("moe_act_rows", (P, self.inter), torch.bfloat16)
-            K.moe_expert_mma(xs, self.w_gu, idx, P, yb, True, self.limit, self.slope, self.out_scale,
-                             None if self.on_input else wts, up_offset=self.up_offset)
             rows = ctx.ws.get("moe_rows_out", (P, self.hidden), torch.float32)
-            K.moe_expert_mma(yb, self.w_d, idx, P, rows, False)
-            K.moe_combine(rows, None, residual, T, self.top, ctx.seq_of_token)
+            flat_idx, flat_wts = idx.view(-1), wts.view(-1)
+            for p0 in range(0, P, K.MOE_MMA_MAX_PAIRS):
+                p1 = min(P, p0 + K.MOE_MMA_MAX_PAIRS)
+                K.moe_expert_mma(xs[p0:p1], self.w_gu, flat_idx[p0:p1], p1 - p0, yb[p0:p1], True, self.limit, self.slope,
+                                 self.out_scale, None if self.on_input else flat_wts[p0:p1], up_offset=self.up_offset)
+                K.moe_expert_mma(yb[p0:p1], self.w_d, flat_idx[p0:p1], p1 - p0, rows[p0:p1], False)
+            K.moe_combine(rows, None, residual, T, self.top, ctx.seq_of_token, idx=idx if self.identity else None)
             return
         y = ctx.ws.get("moe_act", (T * self.top, self.inter), torch.float32)
         K.moe_gate_up(h, self.w_gu, idx, wts, y, T, self.top, self.on_input, self.limit, self.slope, self.out_scale,

@@ -60,7 +60,7 @@ class _Grouped:
             if n:
                 self.down[e](y[off[e]:off[e + 1]], out[off[e]:off[e + 1]], m=n, ws=ws)
         kernel("moe", "gg_moe_combine")(out.data_ptr(), place.data_ptr(), residual.data_ptr(), T, W, top,
-                                        ctx.seq_of_token.data_ptr(), _s())
+                                        ctx.seq_of_token.data_ptr(), 0, _s())
 
 
 def try_make(part) -> Optional[_Grouped]:

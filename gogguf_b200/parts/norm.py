@@ -39,3 +39,34 @@ class RMSNorm:
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         """x: float32 rows of the residual stream; out: compute dtype; rows: optional row gather."""
         K.rmsnorm(x, self.weight, self.eps, out, rows)
+
+
+@register_norm("group_rmsnorm")
+class GroupRMSNorm:
+    """RMS norm in groups: the row is cut into `groups` equal consecutive runs, each is divided by its own
+    sqrt(mean(run^2) + eps), and the whole is multiplied by the stored weight.  ``scale_tensor`` (optional) names a
+    second stored vector of the row's size that multiplies the result element by element (a layer scale); the two
+    vectors are multiplied once, in float32, when the model is built.  With one group and no scale this is
+    `rmsnorm`; it is not offered to a product as a folded norm."""
+
+    foldable = False
+
+    @classmethod
+    def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
+        t = {spec.get("tensor", "weight"): TensorDecl(shape=(spec["size"],), init="ones_normal")}
+        if spec.get("scale_tensor"):
+            t[spec["scale_tensor"]] = TensorDecl(shape=(spec["size"],), init="ones_normal")
+        return t
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.groups = int(spec.get("groups", 1))
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"group_rmsnorm: {self.size} columns do not form {self.groups} equal runs")
+        self.weight = rt.vector(weights[spec.get("tensor", "weight")])
+        if spec.get("scale_tensor"):
+            self.weight = (self.weight * rt.vector(weights[spec["scale_tensor"]])).contiguous()
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        K.rmsnorm(x, self.weight, self.eps, out, rows, groups=self.groups)

@@ -82,3 +82,11 @@ class RotaryAdjacent(RotaryNeoX):
     kernel that applies them, and a mixer states the pairing it implements in `pairing`."""
 
     pairing = "adjacent"
+
+
+@register_position("rope_yarn_adjacent")
+class RotaryYarnAdjacent(RotaryYarn):
+    """The stretched frequencies and the magnitude of `rope_yarn` with the other pairing: element 2i turns with
+    element 2i + 1.  The tables are those of `RotaryYarn` (column i is pair i)."""
+
+    pairing = "adjacent"

@@ -15,8 +15,10 @@ Interfaces (duck-typed; see `gogguf_b200.parts.base` for the step context they r
 * gate:         ``logits(h, ctx) -> float32 [T, size]`` (workspace memory, valid until the gate is asked again) and
                 an attribute ``bias`` (float32 [size] or None): what an arrangement multiplies a part's output by,
                 element by element, after a sigmoid of logits + bias.
+* stream:       ``begin(x, ctx)`` before a block's parts and ``finish(x, ctx)`` after them: what a block does to the
+                float32 stream `x[T, hidden]` as a whole (a weighted sum with what earlier blocks left).
 * position:     built by the mixer that uses it from ``spec["position"]``; ``tables(ctx)``.
-* arrangement:  class attribute ``roles = {role: family}`` (family "mixer", "feed_forward" or "norm"; optional
+* arrangement:  class attribute ``roles = {role: family}`` (family "mixer", "feed_forward", "norm", "gate" or "stream"; optional
                 ``optional_roles``), ``__init__(block_spec, parts, runtime)`` with `parts` the built parts by role,
                 an attribute ``parts`` holding them, and ``forward(x, ctx, cache, writes_cache)``.
 * any part may set ``capturable = False`` if its `forward` reads back to the host or allocates; a model with
@@ -30,6 +32,7 @@ MIXERS: Dict[str, Type] = {}
 FEED_FORWARDS: Dict[str, Type] = {}
 NORMS: Dict[str, Type] = {}
 GATES: Dict[str, Type] = {}
+STREAMS: Dict[str, Type] = {}
 POSITIONS: Dict[str, Type] = {}
 ARRANGEMENTS: Dict[str, Type] = {}
 EMBEDDINGS: Dict[str, Type] = {}
@@ -51,6 +54,7 @@ register_mixer = _register(MIXERS, "mixer")
 register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_gate = _register(GATES, "gate")
+register_stream = _register(STREAMS, "stream operation")
 register_position = _register(POSITIONS, "position encoding")
 register_arrangement = _register(ARRANGEMENTS, "block arrangement")
 register_embedding = _register(EMBEDDINGS, "embedding")

@@ -41,7 +41,8 @@ class TensorDecl:
     """What a part expects of one tensor.
 
     init: "normal" (N(0, std)), "ones_normal" (1 + N(0, norm_std)), "zeros_normal" (N(0, norm_std)),
-    "small_normal" (N(0, 0.5)), "unit_interval" (sigmoid of N(0, 1): numbers inside (0, 1)) or "zeros";
+    "small_normal" (N(0, 0.5)), "unit_interval" (sigmoid of N(0, 1): numbers inside (0, 1)), "mean" ((1 + N(0,
+    norm_std)) / n for a vector of n: the coefficients of an average) or "zeros";
     used only by the random-weights mode.  optional: may be absent (for
     instance a separate head matrix of a model with tied embeddings).
     """
@@ -164,6 +165,8 @@ def random_tensors(expected: Mapping[str, TensorDecl], seed: int, std: float, no
                 t.mul_(0.5)
             elif d.init == "unit_interval":      # lower bounds of a gate
                 t.sigmoid_()
+            elif d.init == "mean":               # coefficients of an average
+                t.mul_(norm_std).add_(1.0).div_(float(d.shape[-1]))
             else:
                 raise ValueError(f"tensor {name!r}: unknown init {d.init!r}")
         out[name] = t.to(dtype)
