@@ -89,7 +89,10 @@ class RotationConfig:
         scaling = None
         if sc is not None:
             scaling = tuple(_number(sc, k, where + ".scaling") for k in ("factor", "original", "fast", "slow"))
-        return cls(dims=dims, base=_number(d, "base", where) if dims else 0.0, scaling=scaling)
+        base = _number(d, "base", where) if dims or (isinstance(d, dict) and d.get("base") is not None) else 0.0
+        if dims and not base > 1.0:
+            raise ConfigError(f"dinuzen config: {where}.base must be above one, got {base}")
+        return cls(dims=dims, base=base, scaling=scaling)
 
     def to_dict(self) -> Dict[str, Any]:
         d: Dict[str, Any] = dict(dims=self.dims, base=self.base)
@@ -140,7 +143,8 @@ class MixerConfig:
             heads, kv = _pos_int(d, "heads", where), _pos_int(d, "kv_heads", where)
             if heads % kv:
                 raise ConfigError(f"dinuzen config: {where}: {heads} heads are not a multiple of {kv} kv_heads")
-            rot = RotationConfig.from_dict(_need(d, "rot", where), where + ".rot")
+            rot = (RotationConfig.from_dict(d["rot"], where + ".rot") if d.get("rot") is not None
+                   else RotationConfig(dims=0, base=0.0))       # no rotation where the layer names none
             dim = _pos_int(d, "dim", where)
             if rot.dims > dim:
                 raise ConfigError(f"dinuzen config: {where}.rot.dims={rot.dims} exceeds dim={dim}")
@@ -153,7 +157,8 @@ class MixerConfig:
                 raise ConfigError(f"dinuzen config: {where}: a width of {width} does not form {blocks} equal blocks")
             return cls(width=width, blocks=blocks, conv=_pos_int(d, "conv", where))
         heads, groups = _pos_int(d, "heads", where), _pos_int(d, "groups", where)
-        vdim, ng = _pos_int(d, "vdim", where), _pos_int(d, "norm_groups", where)
+        vdim = _pos_int(d, "vdim", where)
+        ng = _pos_int(d, "norm_groups", where) if d.get("norm_groups") is not None else 1
         if heads % groups:
             raise ConfigError(f"dinuzen config: {where}: {heads} heads do not form {groups} equal groups")
         if (heads * vdim) % ng:
