@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload] [--prefill-lengths 256,1024] [--decode-contexts 16384,32768]
-    python bench.py --compare gigopel|sokirax|felolorn [--compare-sizes 2k,4k]   (another workload, see the end of this text)
+    python bench.py --compare gigopel|sokirax|felolorn|dinuzen [--compare-sizes 2k,4k]   (another workload, see the end of this text)
 
 A "step" is one decode step of a batch: every sequence goes on by one token, sampled greedily on the
 device.  The timed region is exactly K steps after W warm-up steps, timed with CUDA events on the
@@ -38,6 +38,14 @@ output, a short convolution before the mixer; latent attention with a query late
 or HGRN2; experts chosen inside the best groups): an all-experts model per size whose layers cycle through the three
 mixers, beside the all-experts Sokirax model (its closest relative: the same arrangement of norms, retention,
 routed experts) and the same Qwen3.  It prints {"compare": "felolorn", "sizes": {...}}.
+
+`--compare dinuzen` measures the Dinuzen design (a norm in groups on every part's output with a layer scale, a
+token shift before the mixer, a weighted sum over depth after every layer; differential attention, of which every
+second layer reads the keys and values of the one before, the recurrent block with a real-gated linear recurrent
+unit, Mamba-2; routed experts with identity experts and a gated shared expert): an all-experts model per size whose
+layers cycle through attention, RG-LRU, Mamba-2 and attention on borrowed keys, beside the all-experts Felolorn model
+(its closest relative: norms after the parts, recurrences behind short convolutions, routed experts with a
+correction) and the same Qwen3.  It prints {"compare": "dinuzen", "sizes": {...}}.
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures of an earlier measurement on this pool.  The weights (16 GB) are far larger than
@@ -243,6 +251,45 @@ def felolorn_config(z):
                 layers=[dict(type=mixers[i % 3][0], mixer=mixers[i % 3][1], mlp=mlp) for i in range(z["layers"])])
 
 
+# Dinuzen at the same widths and depths: differential attention with two maps of 64 (2k) or 128 (4k) per head over
+# values of 128, a recurrent unit as wide as the stream in 16 blocks, Mamba-2 heads of 64 with states of 128, the same
+# experts plus identity outputs and a shared expert
+DINUZEN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=64, vdim=128, lru_blocks=16, ssm_heads=32, ssm_vdim=64, ssm_state=128,
+               ssm_groups=8, taps=4, norm_groups=8, experts=16, identity=2, top=2, expert_ff=1024, shared_ff=1024, layers=8,
+               vocab=65536),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, lru_blocks=16, ssm_heads=64, ssm_vdim=64, ssm_state=128,
+               ssm_groups=8, taps=4, norm_groups=8, experts=32, identity=4, top=4, expert_ff=2048, shared_ff=2048, layers=8,
+               vocab=65536),
+}
+
+
+def dinuzen_config(z):
+    """Layers cycle through differential attention, RG-LRU, Mamba-2 and differential attention on the keys and values
+    of the attention layer three places before; every layer has routed experts."""
+    W = z["width"]
+    rot = dict(dims=z["dim"] // 2, base=500000.0, scaling=dict(factor=4.0, original=8192, fast=16.0, slow=2.0))
+    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5, softcap=30.0,
+               diff=0.3, rot=rot)
+    mlp = dict(kind="moe", expert=dict(ff=z["expert_ff"]),
+               router=dict(experts=z["experts"], identity=z["identity"], top=z["top"], scale=1.5), shared=dict(ff=z["shared_ff"]))
+    layers = []
+    for i in range(z["layers"]):
+        k = i % 4
+        if k == 0:
+            layers.append(dict(type="attention", mixer=dict(att), mlp=mlp))
+        elif k == 1:
+            layers.append(dict(type="rglru", mixer=dict(width=W, blocks=z["lru_blocks"], conv=z["taps"]), mlp=mlp))
+        elif k == 2:
+            layers.append(dict(type="mamba2", mixer=dict(heads=z["ssm_heads"], vdim=z["ssm_vdim"], state=z["ssm_state"],
+                                                         groups=z["ssm_groups"], norm_groups=z["ssm_groups"], conv=z["taps"]),
+                               mlp=mlp))
+        else:
+            layers.append(dict(type="attention", mixer=dict(att, kv_from=i - 3), mlp=mlp))
+    return dict(architecture="Dinuzen", vocab=z["vocab"], width=W, norm=dict(eps=1e-6, groups=z["norm_groups"]),
+                initializer_range=0.02, layers=layers)
+
+
 def qwen3_like(z):
     """Qwen3 at the same width, depth, head count and feed-forward parameter count (3 matrices instead of 2), with
     full attention (its cache of a 2,048-token context is read whole; Gigopel reads its window)."""
@@ -372,12 +419,37 @@ def compare_run(a):
         per_seq = n[1] * t * R * 2 + (n[0] + n[2]) * 2 * S * 128 * 128 * 4
         return flops, wbytes, per_seq
 
+    def din_numbers(z, t):
+        """The same figures for a Dinuzen model whose layers cycle through attention, RG-LRU, Mamba-2 and attention on
+        borrowed keys and values."""
+        W, H, G, d, dv = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+        n = [len(range(k, z["layers"], 4)) for k in range(4)]
+        aq = H * 2 * d * W + W * H * dv                        # queries and the output matrix
+        akv = G * (2 * d + dv) * W
+        bw = W // z["lru_blocks"]
+        lr = 3 * W * W + 2 * W * bw                            # y, x, the output matrix, the two gates' blocks
+        inner, gn = z["ssm_heads"] * z["ssm_vdim"], z["ssm_groups"] * z["ssm_state"]
+        ss = (2 * inner + 2 * gn + z["ssm_heads"]) * W + W * inner
+        ff_active = (z["top"] * z["expert_ff"] + z["shared_ff"]) * 3 * W + (z["experts"] + z["identity"] + 1) * W
+        ff_read = (z["experts"] * z["expert_ff"] + z["shared_ff"]) * 3 * W + (z["experts"] + z["identity"] + 1) * W
+        keys = t * (t + 1) // 2
+        mix = (n[0] + n[3]) * aq + n[0] * akv + n[1] * lr + n[2] * ss
+        attn = (n[0] + n[3]) * 2 * H * (2 * d + 2 * dv) * keys + n[2] * t * z["ssm_heads"] * 2 * 2 * z["ssm_state"] * z["ssm_vdim"]
+        flops = 2 * t * (mix + z["layers"] * ff_active) + attn + 2 * z["vocab"] * W
+        wbytes = (mix + z["layers"] * ff_read) * 2 + z["vocab"] * W * 2
+        per_seq = (n[0] + n[3]) * t * G * (2 * d + dv) * 2 + n[2] * 2 * inner * z["ssm_state"] * 4 + n[1] * 2 * W * 4
+        return flops, wbytes, per_seq
+
     out = {}
     T = PROMPT_LEN
     design = a.compare
     for name in [x for x in a.compare_sizes.split(",") if x.strip()]:
         z = GIGOPEL_SIZES[name]
-        if design == "felolorn":
+        if design == "dinuzen":
+            zs, zf, zd = SOKIRAX_SIZES[name], FELOLORN_SIZES[name], DINUZEN_SIZES[name]
+            arms = [("dinuzen_experts", dinuzen_config(zd)), ("felolorn_experts", felolorn_config(zf)),
+                    ("qwen3_like", qwen3_like(z))]
+        elif design == "felolorn":
             zs, zf = SOKIRAX_SIZES[name], FELOLORN_SIZES[name]
             arms = [("felolorn_experts", felolorn_config(zf)), ("sokirax_experts", sokirax_config(zs, "moe")),
                     ("qwen3_like", qwen3_like(z))]
@@ -396,6 +468,8 @@ def compare_run(a):
             per_seq = 0
             if arm == "qwen3_like":
                 flops, wbytes = qwen_numbers(cd, z, T)
+            elif arm == "dinuzen_experts":
+                flops, wbytes, per_seq = din_numbers(zd, T)
             elif arm == "felolorn_experts":
                 flops, wbytes, per_seq = fel_numbers(zf, T)
             elif design in ("sokirax", "felolorn"):
@@ -411,12 +485,12 @@ def compare_run(a):
                 dms, kernels = decode_ms(model, b, T, max(16, min(a.steps, 64)), max(a.warmup, 3))
                 # experts: a step reads at most batch * top experts' matrices, not all of them
                 rb = wbytes
-                if arm in ("gigopel_experts", "sokirax_experts", "felolorn_experts"):
+                if arm in ("gigopel_experts", "sokirax_experts", "felolorn_experts", "dinuzen_experts"):
                     used = min(z["experts"], b * z["top"])
                     rb -= z["layers"] * (z["experts"] - used) * 3 * z["width"] * z["expert_ff"] * 2
                 if arm == "qwen3_like":
                     rb += b * T * 2 * z["layers"] * 8 * 128 * 2
-                elif design in ("sokirax", "felolorn"):
+                elif design in ("sokirax", "felolorn", "dinuzen"):
                     rb += b * per_seq
                 else:
                     rb += b * min(T, z["window"]) * z["layers"] * (z["kv_rank"] + z["rot_dim"]) * 2
@@ -455,7 +529,7 @@ def main():
                     "decode_by_context)")
     ap.add_argument("--prefill-lengths", default="", help="comma separated prompt lengths: time one prefill step of each "
                     "(printed on stderr, added to the line as prefill_sweep)")
-    ap.add_argument("--compare", default="", choices=["", "gigopel", "sokirax", "felolorn"],
+    ap.add_argument("--compare", default="", choices=["", "gigopel", "sokirax", "felolorn", "dinuzen"],
                     help="another workload: the named design beside Qwen3 at equal size (prefill and decode), see the top")
     ap.add_argument("--compare-sizes", default="2k,4k", help="which of the comparison's layer sizes to run")
     a = ap.parse_args()

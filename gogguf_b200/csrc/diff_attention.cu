@@ -224,5 +224,288 @@ GG_API gg_diff_attention(const void* q, const void* k_pool, const void* v_pool, 
     return gg_last_error();
 }
 
+// ----------------------------------------------------------------------------- the same on the tensor cores (bfloat16)
+// A CTA of four warps takes 64 query rows: the hpg = heads / kv_heads query heads of one kv head for tpt = 64 / hpg
+// consecutive tokens of one sequence (row r: token r / hpg, head r % hpg), so the keys and values of a page are
+// read once for all heads that share them.  The key tiles are the sequence's pages (64 positions: [64][2 d] keys
+// with both maps side by side, [64][dv] values), brought into shared memory by cp.async in two stages.  Per tile
+// and map: S = Q_m K_m^T (mma.sync m16n8k16, fragments by ldmatrix), scale, bound and mask in float32, an online
+// softmax per row and map in float32, P rounded to bfloat16 as the A operand of O_m += P V (V fragments by
+// ldmatrix.trans).  At the end out = out_scale * unit(O_1 / l_1 - lambda O_2 / l_2) per row.  Prompts, portions
+// and decode steps take this kernel; page_size must be 64, d and dv one of 32, 64, 128.
+__device__ __forceinline__ void da_ldsm4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void da_ldsm4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void da_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void da_cp16(void* dst, const void* src) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(a), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t da_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float da_quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float da_quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+#define DA_ROWS 64
+#define DA_KEYS 64
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128) diff_attention_mma_kernel(
+    const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* out, const int* __restrict__ positions,
+    const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens, const int* __restrict__ page_table,
+    int max_pages, int n_seqs, int H, int G, int hpg, int tpt, float scale, float cap, int window, float lambda,
+    float eps, float out_scale, const PageBounds pb) {
+    pdl_wait();
+    constexpr int QS = 2 * D + 8, KS = 2 * D + 8, VS = DV + 8;     // row strides in elements (16 bytes of padding)
+    extern __shared__ __align__(16) unsigned char da_smem[];
+    bf16* Qs = reinterpret_cast<bf16*>(da_smem);                    // [64][QS]
+    bf16* Ks = Qs + DA_ROWS * QS;                                   // [2][64][KS]
+    bf16* Vs = Ks + 2 * DA_KEYS * KS;                               // [2][64][VS]
+    __shared__ int info[3];
+    const int g = blockIdx.y;
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, b = 0, found = 0;
+        for (; b < n_seqs; ++b) {
+            const int n = cu_seqlens[b + 1] - cu_seqlens[b];
+            const int nt = (n + tpt - 1) / tpt;
+            if (tile < nt) { found = 1; break; }
+            tile -= nt;
+        }
+        info[0] = found ? b : -1;
+        info[1] = found ? cu_seqlens[b] + tile * tpt : 0;
+        info[2] = found ? min(tpt, cu_seqlens[b + 1] - (cu_seqlens[b] + tile * tpt)) : 0;
+    }
+    __syncthreads();
+    const int b = info[0], t0 = info[1], ntok = info[2];
+    if (b < 0) return;
+    const int nrows = ntok * hpg;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (seq_of_token[t0] < 0) {                                     // padding rows of a replayed batch: zeros
+        for (int idx = threadIdx.x; idx < nrows * DV; idx += blockDim.x) {
+            const int r = idx / DV, c = idx - r * DV;
+            out[((size_t)(t0 + r / hpg) * H + g * hpg + r % hpg) * DV + c] = __float2bfloat16_rn(0.f);
+        }
+        return;
+    }
+    // the query rows, both maps side by side
+    for (int idx = threadIdx.x; idx < DA_ROWS * (2 * D / 8); idx += blockDim.x) {
+        const int r = idx / (2 * D / 8), c8 = idx - r * (2 * D / 8);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < nrows)
+            v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r / hpg) * H + g * hpg + r % hpg) * (2 * D) + c8 * 8);
+        *reinterpret_cast<uint4*>(Qs + r * QS + c8 * 8) = v;
+    }
+    const int pos0 = positions[t0];
+    const int pos_last = pos0 + ntok - 1;
+    const int lo_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int j_lo = lo_key / DA_KEYS, j_hi = pos_last / DA_KEYS;
+    const int* pt = page_table + (size_t)b * max_pages;
+
+    auto load_tile = [&](int j, int stage) {
+        const int page = gg_page(pt, j, max_pages, pb, 51);
+        const bf16* kp = k_pool + ((size_t)page * G + g) * DA_KEYS * (2 * D);
+        const bf16* vp = v_pool + ((size_t)page * G + g) * DA_KEYS * DV;
+        bf16* kd = Ks + stage * DA_KEYS * KS;
+        bf16* vd = Vs + stage * DA_KEYS * VS;
+        for (int idx = threadIdx.x; idx < DA_KEYS * (2 * D / 8); idx += blockDim.x) {
+            const int r = idx / (2 * D / 8), c8 = idx - r * (2 * D / 8);
+            da_cp16(kd + r * KS + c8 * 8, kp + (size_t)r * (2 * D) + c8 * 8);
+        }
+        for (int idx = threadIdx.x; idx < DA_KEYS * (DV / 8); idx += blockDim.x) {
+            const int r = idx / (DV / 8), c8 = idx - r * (DV / 8);
+            da_cp16(vd + r * VS + c8 * 8, vp + (size_t)r * DV + c8 * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    // this thread's two rows of its warp's sixteen
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int rA = warp * 16 + gq, rB = rA + 8;
+    const int posA = rA < nrows ? pos0 + rA / hpg : -1, posB = rB < nrows ? pos0 + rB / hpg : -1;
+    const int loA = window > 0 ? posA - window + 1 : 0, loB = window > 0 ? posB - window + 1 : 0;
+    const int wlast = min(warp * 16 + 15, nrows - 1);
+    const int wmax = warp * 16 < nrows ? pos0 + wlast / hpg : -1;   // the warp's largest position (-1: no rows)
+    float O[2][DV / 8][4];
+    float mrun[2][2], lrun[2][2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        mrun[m][0] = mrun[m][1] = -INFINITY;
+        lrun[m][0] = lrun[m][1] = 0.f;
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n) { O[m][n][0] = O[m][n][1] = O[m][n][2] = O[m][n][3] = 0.f; }
+    }
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+
+    load_tile(j_lo, 0);
+    for (int j = j_lo; j <= j_hi; ++j) {
+        const int stage = (j - j_lo) & 1;
+        if (j < j_hi) {
+            load_tile(j + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int key0 = j * DA_KEYS;
+        if (key0 <= wmax) {
+            const bf16* Kt = Ks + stage * DA_KEYS * KS;
+            const bf16* Vt = Vs + stage * DA_KEYS * VS;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                float s[8][4];
+#pragma unroll
+                for (int n = 0; n < 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    uint32_t a0, a1, a2, a3;
+                    da_ldsm4(a0, a1, a2, a3, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + m * D + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        uint32_t b0, b1, b2, b3;
+                        da_ldsm4(b0, b1, b2, b3, Kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * KS + m * D + ks * 16 + ((lane >> 3) & 1) * 8);
+                        da_mma(s[2 * np], a0, a1, a2, a3, b0, b1);
+                        da_mma(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                    }
+                }
+                float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + n * 8 + 2 * t4 + (e & 1);
+                        float v = s[n][e] * scale;
+                        if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+                        const bool ok = e < 2 ? (key <= posA && key >= loA) : (key <= posB && key >= loB);
+                        v = ok ? v : -INFINITY;
+                        s[n][e] = v;
+                        if (e < 2) mxA = fmaxf(mxA, v); else mxB = fmaxf(mxB, v);
+                    }
+                }
+                mxA = da_quad_max(mxA);
+                mxB = da_quad_max(mxB);
+                const float nA = fmaxf(mrun[m][0], mxA), nB = fmaxf(mrun[m][1], mxB);
+                const float uA = nA == -INFINITY ? 0.f : nA, uB = nB == -INFINITY ? 0.f : nB;
+                const float cA = expf(mrun[m][0] - uA), cB = expf(mrun[m][1] - uB);
+                mrun[m][0] = nA;
+                mrun[m][1] = nB;
+                float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+                    s[n][0] = expf(s[n][0] - uA); s[n][1] = expf(s[n][1] - uA);
+                    s[n][2] = expf(s[n][2] - uB); s[n][3] = expf(s[n][3] - uB);
+                    sumA += s[n][0] + s[n][1];
+                    sumB += s[n][2] + s[n][3];
+                }
+                lrun[m][0] = lrun[m][0] * cA + sumA;
+                lrun[m][1] = lrun[m][1] * cB + sumB;
+#pragma unroll
+                for (int n = 0; n < DV / 8; ++n) { O[m][n][0] *= cA; O[m][n][1] *= cA; O[m][n][2] *= cB; O[m][n][3] *= cB; }
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint32_t a0 = da_pack(s[2 * kk][0], s[2 * kk][1]), a1 = da_pack(s[2 * kk][2], s[2 * kk][3]);
+                    const uint32_t a2 = da_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = da_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                    for (int np = 0; np < DV / 16; ++np) {
+                        uint32_t b0, b1, b2, b3;
+                        da_ldsm4_t(b0, b1, b2, b3, Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8);
+                        da_mma(O[m][2 * np], a0, a1, a2, a3, b0, b1);
+                        da_mma(O[m][2 * np + 1], a0, a1, a2, a3, b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // the difference of the maps, its root mean square over the head's values, the store
+    const float l1A = da_quad_sum(lrun[0][0]), l1B = da_quad_sum(lrun[0][1]);
+    const float l2A = da_quad_sum(lrun[1][0]), l2B = da_quad_sum(lrun[1][1]);
+    const float i1A = posA >= 0 ? 1.0f / l1A : 0.f, i1B = posB >= 0 ? 1.0f / l1B : 0.f;
+    const float i2A = posA >= 0 ? lambda / l2A : 0.f, i2B = posB >= 0 ? lambda / l2B : 0.f;
+    float ssA = 0.f, ssB = 0.f;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+        O[0][n][0] = O[0][n][0] * i1A - O[1][n][0] * i2A;
+        O[0][n][1] = O[0][n][1] * i1A - O[1][n][1] * i2A;
+        O[0][n][2] = O[0][n][2] * i1B - O[1][n][2] * i2B;
+        O[0][n][3] = O[0][n][3] * i1B - O[1][n][3] * i2B;
+        ssA += O[0][n][0] * O[0][n][0] + O[0][n][1] * O[0][n][1];
+        ssB += O[0][n][2] * O[0][n][2] + O[0][n][3] * O[0][n][3];
+    }
+    ssA = da_quad_sum(ssA);
+    ssB = da_quad_sum(ssB);
+    const float fA = out_scale / sqrtf(ssA / (float)DV + eps), fB = out_scale / sqrtf(ssB / (float)DV + eps);
+    if (posA >= 0) {
+        bf16* o = out + ((size_t)(t0 + rA / hpg) * H + g * hpg + rA % hpg) * DV;
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n)
+            *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * t4) = da_pack(O[0][n][0] * fA, O[0][n][1] * fA);
+    }
+    if (posB >= 0) {
+        bf16* o = out + ((size_t)(t0 + rB / hpg) * H + g * hpg + rB % hpg) * DV;
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n)
+            *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * t4) = da_pack(O[0][n][2] * fB, O[0][n][3] * fB);
+    }
+}
+
+template <int D, int DV>
+static int da_mma_launch(const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* out, const int* positions,
+                         const int* seq_of_token, const int* cu_seqlens, const int* page_table, int max_pages, int n_pages,
+                         int ntok, int n_seqs, int H, int G, float scale, float cap, int window, float lambda, float eps,
+                         float out_scale, int* status, cudaStream_t stream) {
+    const int hpg = H / G;
+    const int tpt = DA_ROWS / hpg;
+    const size_t smem = ((size_t)DA_ROWS * (2 * D + 8) + 2 * DA_KEYS * (2 * D + 8) + 2 * DA_KEYS * (DV + 8)) * sizeof(bf16);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(diff_attention_mma_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int tiles = (ntok + tpt - 1) / tpt + n_seqs;             // an upper bound on the sequences' tiles
+    return gg_launch(diff_attention_mma_kernel<D, DV>, dim3(tiles, G), dim3(128), smem, stream, 1, q, k_pool, v_pool, out,
+                     positions, seq_of_token, cu_seqlens, page_table, max_pages, n_seqs, H, G, hpg, tpt, scale, cap, window,
+                     lambda, eps, out_scale, PageBounds{n_pages, status});
+}
+
+// 1 if the tensor-core form takes these sizes (bfloat16 only), else 0.
+GG_API gg_diff_attention_mma_takes(int H, int G, int d, int dv, int page_size) {
+    const bool dims = (d == 32 || d == 64 || d == 128) && (dv == 32 || dv == 64 || dv == 128);
+    return (dims && page_size == DA_KEYS && G > 0 && H % G == 0 && H / G <= DA_ROWS && G <= 65535) ? 1 : 0;
+}
+
+// As gg_diff_attention for bfloat16 tensors, with the step's cu_seqlens [n_seqs + 1].
+GG_API gg_diff_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
+                             const int* seq_of_token, const int* cu_seqlens, const int* page_table, int max_pages,
+                             int page_size, int n_pages, int ntok, int n_seqs, int H, int G, int d, int dv, float scale,
+                             float cap, int window, float lambda, float eps, float out_scale, int* status,
+                             cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (!gg_diff_attention_mma_takes(H, G, d, dv, page_size)) return GG_ERR_ARG;
+#define DA_GO(D_, V_) return da_mma_launch<D_, V_>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, positions, \
+        seq_of_token, cu_seqlens, page_table, max_pages, n_pages, ntok, n_seqs, H, G, scale, cap, window, lambda, eps,      \
+        out_scale, status, stream)
+    if (d == 32) { if (dv == 32) DA_GO(32, 32); if (dv == 64) DA_GO(32, 64); DA_GO(32, 128); }
+    if (d == 64) { if (dv == 32) DA_GO(64, 32); if (dv == 64) DA_GO(64, 64); DA_GO(64, 128); }
+    if (dv == 32) DA_GO(128, 32);
+    if (dv == 64) DA_GO(128, 64);
+    DA_GO(128, 128);
+#undef DA_GO
+}
+
 // 1 if this library was built with checked page tables (the debug build), else 0.
 GG_API gg_diff_attention_checked() { return gg_debug_bounds(); }

@@ -417,6 +417,32 @@ def diff_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
         _stream())
 
 
+def diff_attention_mma_takes(heads: int, kv_heads: int, d: int, dv: int, page_size: int) -> bool:
+    """Does the tensor-core form of differential attention take these sizes (bfloat16 tensors)?"""
+    from .build import module
+    return bool(module("diff_attention").lib.gg_diff_attention_mma_takes(int(heads), int(kv_heads), int(d), int(dv),
+                                                                          int(page_size)))
+
+
+def diff_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                       positions: torch.Tensor, seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor,
+                       page_table: torch.Tensor, page_size: int, n_tokens: int, n_seqs: int, heads: int, kv_heads: int,
+                       d: int, dv: int, scale: float, cap: float, window: int, lam: float, eps: float,
+                       out_scale: float) -> None:
+    """`diff_attention` on the tensor cores (mma.sync) for bfloat16 tensors: the query heads of a kv head and up to
+    64 / (heads / kv_heads) consecutive tokens of a sequence share a CTA and every page they read."""
+    for t, n in ((q, "q"), (k_pool, "k_pool"), (v_pool, "v_pool"), (out, "out")):
+        _need(t, torch.bfloat16, n)
+    if k_pool.shape[-1] != 2 * d or v_pool.shape[-1] != dv or k_pool.shape[1] != kv_heads:
+        raise KernelError("diff_attention_mma: the pools do not fit the heads")
+    from .tcgen05_gemm import status_word
+    kernel("diff_attention", "gg_diff_attention_mma")(
+        _p(q), _p(k_pool), _p(v_pool), _p(out), _p(positions), _p(seq_of_token), _p(cu_seqlens), _p(page_table),
+        page_table.shape[-1], int(page_size), k_pool.shape[0], int(n_tokens), int(n_seqs), int(heads), int(kv_heads),
+        int(d), int(dv), float(scale), float(cap), int(window), float(lam), float(eps), float(out_scale),
+        _p(status_word(q.device)), _stream())
+
+
 # ------------------------------------------------------------------------------- latent attention
 def latent_prep(q: torch.Tensor, dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, cos: torch.Tensor,
                 sin: torch.Tensor, rot_dims: int, positions: torch.Tensor, seq_of_token: torch.Tensor,

@@ -16,11 +16,15 @@ rotation equal this layer's) with queries of its own.
 
 Spec parameters: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, scale, softcap (0 or absent: none),
 diff, eps, window (absent: none), position {kind, ...} (absent or rotary_dim 0: none), kv_source, names.
-Norms, rotation, scores, softmax, the difference and its norm are float32 in both compute paths.
+Norms, rotation, scores, softmax, the difference and its norm are float32 in both compute paths.  In the bfloat16
+path, head sizes of 32, 64 and 128 run on the tensor cores (`csrc/diff_attention.cu`: the softmax weights are
+rounded to bfloat16 for the product with the values, the sums that norm them are not); GOGGUF_B200_DIFF_ATTN_MMA=0
+keeps the plain kernel, its twin.
 """
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional
 
 import torch
@@ -108,6 +112,7 @@ class DiffAttentionMixer:
         lam = [weights[n[key]].detach().double().cpu() for key in ("lq1", "lk1", "lq2", "lk2")]
         self.lam = math.exp(float((lam[0] * lam[1]).sum())) - math.exp(float((lam[2] * lam[3]).sum())) + self.diff
         self.out_scale = 1.0 - self.diff
+        self._mma = (rt.fast and rt.dtype == torch.bfloat16 and os.environ.get("GOGGUF_B200_DIFF_ATTN_MMA", "1") != "0")
 
     def prepare(self, ctx: StepContext) -> None:
         if self.position is not None:
@@ -129,6 +134,11 @@ class DiffAttentionMixer:
                        cache.page_size, cache.k if self.own_kv else None, cache.v if self.own_kv else None, T, H, G, d, dv,
                        self.rot)
         o = ctx.ws.get("diff_attn_out", (T, H * dv), dt)
-        K.diff_attention(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, table, cache.page_size, T, H, G, d, dv,
-                         self.scale, self.cap, self.window, self.lam, self.eps, self.out_scale)
+        if self._mma and K.diff_attention_mma_takes(H, G, d, dv, cache.page_size):
+            K.diff_attention_mma(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, ctx.cu_seqlens, table,
+                                 cache.page_size, T, ctx.n_seqs, H, G, d, dv, self.scale, self.cap, self.window, self.lam,
+                                 self.eps, self.out_scale)
+        else:
+            K.diff_attention(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, table, cache.page_size, T, H, G, d, dv,
+                             self.scale, self.cap, self.window, self.lam, self.eps, self.out_scale)
         self.o(o, residual, accumulate=True, ws=ctx.ws)

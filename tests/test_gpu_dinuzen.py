@@ -166,6 +166,43 @@ def test_choice_of_experts_with_identity_outputs_alone(R, E, top, scale):
     assert float((res.cpu().double() - want).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("H,G,d,dv,window,cap", [(4, 1, 64, 128, 0, 20.0), (8, 2, 32, 64, 0, 0.0), (3, 3, 128, 128, 0, 30.0),
+                                                  (6, 2, 64, 32, 70, 5.0), (5, 1, 32, 32, 0, 10.0), (16, 2, 64, 64, 129, 0.0)])
+def test_differential_attention_on_the_tensor_cores_against_the_plain_kernel(H, G, d, dv, window, cap):
+    """Both kernels on the same cache: prompts of unequal lengths, then portions that go on from the cache, then
+    one token each; pages in no particular order; a window; heads that do not fill a tile evenly."""
+    K = _K()
+    g = _gen(H * d + dv)
+    assert K.diff_attention_mma_takes(H, G, d, dv, 64)
+    n_pages, ps = 40, 64
+    kpool = (torch.randn(n_pages, G, ps, 2 * d, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    vpool = torch.randn(n_pages, G, ps, dv, generator=g).to(torch.bfloat16).to(DEV)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    tables = [perm[0:8], perm[8:16], perm[16:24]]
+    table = _i32(tables)
+    done = [0, 0, 0]
+    for lens in ((130, 1, 67), (65, 200, 2), (1, 1, 1), (1, 1, 1)):
+        cu, sot, cul = _batch(lens)
+        T = sum(lens)
+        pos = _i32([done[b] + i for b, n in enumerate(lens) for i in range(n)])
+        q = torch.randn(T, H * 2 * d, generator=g).to(torch.bfloat16).to(DEV)
+        a = torch.empty(T, H * dv, dtype=torch.bfloat16, device=DEV)
+        b_ = torch.empty_like(a)
+        K.diff_attention(q, kpool, vpool, a, pos, sot, table, ps, T, H, G, d, dv, 0.11, cap, window, 0.37, 1e-6, 0.8)
+        K.diff_attention_mma(q, kpool, vpool, b_, pos, sot, cu, table, ps, T, 3, H, G, d, dv, 0.11, cap, window, 0.37, 1e-6, 0.8)
+        err = (a.float() - b_.float()).abs().max(dim=-1).values / a.float().abs().max()
+        assert float(err.max()) < 3e-2 and float(err.median()) < 1e-2, (float(err.max()), float(err.median()), lens)   # (an output rounds to 2^-8 of itself)
+        done = [x + n for x, n in zip(done, lens)]
+    # a padding row (a replayed batch smaller than its graph) gives zeros and reads nothing
+    cu, sot, _ = _batch((1, 1))
+    sot[1] = -1
+    q = torch.randn(2, H * 2 * d, generator=g).to(torch.bfloat16).to(DEV)
+    o = torch.full((2, H * dv), 5.0, dtype=torch.bfloat16, device=DEV)
+    K.diff_attention_mma(q, kpool, vpool, o, _i32([done[0], 0]), sot, cu, table[:2].contiguous(), ps, 2, 2, H, G, d, dv, 0.11, cap,
+                         window, 0.37, 1e-6, 0.8)
+    assert float(o[1].abs().max()) == 0.0 and float(o[0].abs().max()) > 0.0
+
+
 def _one_layer(kind, mixer, mlp=None, width=64, groups=2, vocab=61, eps=1e-5):
     return model(vocab, width, eps, groups, [layer(kind, mixer, mlp)])
 
