@@ -230,8 +230,8 @@ GG_API gg_diff_attention(const void* q, const void* k_pool, const void* v_pool, 
 // read once for all heads that share them.  The key tiles are the sequence's pages (64 positions: [64][2 d] keys
 // with both maps side by side, [64][dv] values), brought into shared memory by cp.async in two stages.  Per tile
 // and map: S = Q_m K_m^T (mma.sync m16n8k16, fragments by ldmatrix), scale, bound and mask in float32, an online
-// softmax per row and map in float32, P rounded to bfloat16 as the A operand of O_m += P V (V fragments by
-// ldmatrix.trans).  At the end out = out_scale * unit(O_1 / l_1 - lambda O_2 / l_2) per row.  Prompts, portions
+// softmax per row and map in float32, P as the A operand of O_m += P V in two bfloat16 terms (its rounding and
+// what the rounding left out, so that the weights enter with sixteen bits and more; V fragments by ldmatrix.trans).  At the end out = out_scale * unit(O_1 / l_1 - lambda O_2 / l_2) per row.  Prompts, portions
 // and decode steps take this kernel; page_size must be 64, d and dv one of 32, 64, 128.
 __device__ __forceinline__ void da_ldsm4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
@@ -254,6 +254,13 @@ __device__ __forceinline__ void da_cp16(void* dst, const void* src) {
 __device__ __forceinline__ uint32_t da_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
+}
+// (x, y) as a pair of bfloat16 numbers `hi` and the pair `lo` of what that rounding left out
+__device__ __forceinline__ void da_split(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    const float2 hf = __bfloat1622float2(h);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = da_pack(x - hf.x, y - hf.y);
 }
 __device__ __forceinline__ float da_quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
@@ -420,14 +427,21 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
                 for (int n = 0; n < DV / 8; ++n) { O[m][n][0] *= cA; O[m][n][1] *= cA; O[m][n][2] *= cB; O[m][n][3] *= cB; }
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    const uint32_t a0 = da_pack(s[2 * kk][0], s[2 * kk][1]), a1 = da_pack(s[2 * kk][2], s[2 * kk][3]);
-                    const uint32_t a2 = da_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = da_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+                    // the weights as two bfloat16 terms, p = hi + lo, so that the product with the values takes them
+                    // to sixteen bits and more
+                    uint32_t ah[4], al[4];
+                    da_split(s[2 * kk][0], s[2 * kk][1], ah[0], al[0]);
+                    da_split(s[2 * kk][2], s[2 * kk][3], ah[1], al[1]);
+                    da_split(s[2 * kk + 1][0], s[2 * kk + 1][1], ah[2], al[2]);
+                    da_split(s[2 * kk + 1][2], s[2 * kk + 1][3], ah[3], al[3]);
 #pragma unroll
                     for (int np = 0; np < DV / 16; ++np) {
                         uint32_t b0, b1, b2, b3;
                         da_ldsm4_t(b0, b1, b2, b3, Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8);
-                        da_mma(O[m][2 * np], a0, a1, a2, a3, b0, b1);
-                        da_mma(O[m][2 * np + 1], a0, a1, a2, a3, b2, b3);
+                        da_mma(O[m][2 * np], ah[0], ah[1], ah[2], ah[3], b0, b1);
+                        da_mma(O[m][2 * np + 1], ah[0], ah[1], ah[2], ah[3], b2, b3);
+                        da_mma(O[m][2 * np], al[0], al[1], al[2], al[3], b0, b1);
+                        da_mma(O[m][2 * np + 1], al[0], al[1], al[2], al[3], b2, b3);
                     }
                 }
             }

@@ -17,8 +17,8 @@ rotation equal this layer's) with queries of its own.
 Spec parameters: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, scale, softcap (0 or absent: none),
 diff, eps, window (absent: none), position {kind, ...} (absent or rotary_dim 0: none), kv_source, names.
 Norms, rotation, scores, softmax, the difference and its norm are float32 in both compute paths.  In the bfloat16
-path, head sizes of 32, 64 and 128 run on the tensor cores (`csrc/diff_attention.cu`: the softmax weights are
-rounded to bfloat16 for the product with the values, the sums that norm them are not); GOGGUF_B200_DIFF_ATTN_MMA=0
+path, head sizes of 32, 64 and 128 run on the tensor cores (`csrc/diff_attention.cu`: the softmax weights enter the
+product with the values as two bfloat16 terms, the sums that norm them are float32); GOGGUF_B200_DIFF_ATTN_MMA=0
 keeps the plain kernel, its twin.
 """
 from __future__ import annotations
