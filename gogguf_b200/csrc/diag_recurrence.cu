@@ -121,3 +121,112 @@ GG_API gg_diag_scan(const float* a, const float* b, const void* y, long long ldy
                   (T*)out, state, cu_seqlens, slots, seq_of_token, C));
     return gg_last_error();
 }
+
+// ----------------------------------------------------------------------------- prompts in chunks
+// The same recurrence cut into chunks of DG_CHUNK rows, every (chunk, channel) a thread of its own, in three
+// kernels.  Inside a chunk that starts from S_in:  S_t = P_t S_in + L_t,  P_t = a_first ... a_t,  L_t the chunk's own
+// scan from zero.
+//   1. diag_chunk_sums_kernel:  A_c = P_last and B_c = L_last of every chunk
+//   2. diag_chunk_walk_kernel:  S_in(c + 1) = A_c S_in(c) + B_c along a sequence's chunks, from the slot's state and
+//                               into it; every chunk's S_in is left in scratch
+//   3. diag_chunk_out_kernel:   the chunk's rows again from S_in, out_t = S_t * gelu(y_t + ybias)
+// The sums are those of the row-by-row walk in another bracketing, so what a position gets does not depend on how
+// its prompt was cut beyond rounding.  Chunks never cross sequences: chunk k of the step's list belongs to the
+// sequence b whose chunks' running count passes k.
+#define DG_CHUNK 64
+
+__device__ __forceinline__ bool diag_find_chunk(const int* __restrict__ cu_seqlens, int n_seqs, int k, int& b, int& t0, int& t1) {
+    for (b = 0; b < n_seqs; ++b) {
+        const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+        const int nc = (n + DG_CHUNK - 1) / DG_CHUNK;
+        if (k < nc) {
+            t0 = start + k * DG_CHUNK;
+            t1 = min(t0 + DG_CHUNK, start + n);
+            return true;
+        }
+        k -= nc;
+    }
+    return false;
+}
+
+// grid (chunks, ceil(C / 256)); sums [chunks][2][C]
+__global__ void __launch_bounds__(256) diag_chunk_sums_kernel(const float* a, const float* b, float* sums,
+                                                              const int* __restrict__ cu_seqlens, int n_seqs, int C) {
+    pdl_launch();
+    pdl_wait();
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    int sq, t0, t1;
+    if (ch >= C || !diag_find_chunk(cu_seqlens, n_seqs, blockIdx.x, sq, t0, t1)) return;
+    float A = 1.f, B = 0.f;
+#pragma unroll 8
+    for (int t = t0; t < t1; ++t) {
+        const float at = a[(size_t)t * C + ch];
+        B = fmaf(at, B, b[(size_t)t * C + ch]);
+        A *= at;
+    }
+    sums[((size_t)blockIdx.x * 2) * C + ch] = A;
+    sums[((size_t)blockIdx.x * 2 + 1) * C + ch] = B;
+}
+
+// grid (sequence, ceil(C / 256)); sums[k][0] is overwritten by the chunk's S_in
+__global__ void __launch_bounds__(256) diag_chunk_walk_kernel(float* sums, float* state, const int* __restrict__ cu_seqlens,
+                                                              const int* __restrict__ slots,
+                                                              const int* __restrict__ seq_of_token, int C) {
+    pdl_launch();
+    pdl_wait();
+    const int s = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    const int start = cu_seqlens[s], end = cu_seqlens[s + 1];
+    if (ch >= C || end <= start || seq_of_token[start] < 0) return;
+    int k0 = 0;
+    for (int b = 0; b < s; ++b) k0 += (cu_seqlens[b + 1] - cu_seqlens[b] + DG_CHUNK - 1) / DG_CHUNK;
+    const int nc = (end - start + DG_CHUNK - 1) / DG_CHUNK;
+    float* sp = state + (size_t)slots[s] * C + ch;
+    float S = *sp;
+    for (int k = k0; k < k0 + nc; ++k) {
+        const float A = sums[((size_t)k * 2) * C + ch], B = sums[((size_t)k * 2 + 1) * C + ch];
+        sums[((size_t)k * 2) * C + ch] = S;
+        S = fmaf(A, S, B);
+    }
+    *sp = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) diag_chunk_out_kernel(const float* a, const float* b, const float* sums, const T* y,
+                                                             long long ldy, const float* __restrict__ ybias, T* out,
+                                                             const int* __restrict__ cu_seqlens,
+                                                             const int* __restrict__ seq_of_token, int n_seqs, int C) {
+    pdl_launch();
+    pdl_wait();
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    int sq, t0, t1;
+    if (ch >= C || !diag_find_chunk(cu_seqlens, n_seqs, blockIdx.x, sq, t0, t1)) return;
+    if (seq_of_token[t0] < 0) {
+        for (int t = t0; t < t1; ++t) out[(size_t)t * C + ch] = from_f<T>(0.f);
+        return;
+    }
+    float S = sums[((size_t)blockIdx.x * 2) * C + ch];
+    const float yb = ybias != nullptr ? ybias[ch] : 0.f;
+#pragma unroll 8
+    for (int t = t0; t < t1; ++t) {
+        S = fmaf(a[(size_t)t * C + ch], S, b[(size_t)t * C + ch]);
+        out[(size_t)t * C + ch] = from_f<T>(S * gelu_tanh_f(to_f<T>(y[(size_t)t * ldy + ch]) + yb));
+    }
+}
+
+// As gg_diag_scan; sums: scratch of (ntok / 64 + n_seqs) * 2 * C floats.
+GG_API gg_diag_scan_chunks(const float* a, const float* b, const void* y, long long ldy, int dtype, const float* ybias,
+                           void* out, float* sums, float* state, const int* cu_seqlens, const int* slots,
+                           const int* seq_of_token, int ntok, int n_seqs, int C, cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (C <= 0 || state == nullptr || sums == nullptr || ldy < C || (C + 255) / 256 > 65535) return GG_ERR_ARG;
+    const int chunks = ntok / DG_CHUNK + n_seqs;
+    const dim3 cgrid(chunks, (C + 255) / 256);
+    gg_launch(diag_chunk_sums_kernel, cgrid, dim3(256), 0, stream, 1, a, b, sums, cu_seqlens, n_seqs, C);
+    gg_launch(diag_chunk_walk_kernel, dim3(n_seqs, (C + 255) / 256), dim3(256), 0, stream, 1, sums, state, cu_seqlens, slots,
+              seq_of_token, C);
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(diag_chunk_out_kernel<T>, cgrid, dim3(256), 0, stream, 1, a, b, (const float*)sums, (const T*)y, ldy, ybias,
+                  (T*)out, cu_seqlens, seq_of_token, n_seqs, C));
+    return gg_last_error();
+}

@@ -1090,7 +1090,8 @@ GG_API gg_group_rmsnorm(const float* x, const int* rows, const float* w, void* o
 }
 
 // x[r, :] += groupnorm(y[r, :]) * w: the norm that follows a part and the add into the stream, all float32.
-// zero_y != 0: y is left zeroed.  One block per row; a run of the row at a time.
+// zero_y != 0: y is left zeroed.  One block per row.  Runs of up to 4,096 numbers are a warp's work each (no block
+// barrier: the warp sums its run, norms it and adds it); longer runs take the whole block, a run at a time.
 __global__ void __launch_bounds__(256) group_rmsnorm_add_kernel(float* x, float* y, const float* __restrict__ w, int H,
                                                                 int groups, float eps, int zero_y) {
     pdl_launch();
@@ -1100,6 +1101,21 @@ __global__ void __launch_bounds__(256) group_rmsnorm_add_kernel(float* x, float*
     float* yr = y + r * H;
     float* xr = x + r * H;
     const int gs = H / groups;
+    if (gs <= 4096) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+        for (int g = warp; g < groups; g += nwarps) {
+            float ss = 0.f;
+            for (int i = lane; i < gs; i += 32) { const float v = yr[g * gs + i]; ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            const float f = 1.0f / sqrtf(ss / (float)gs + eps);
+            for (int i = lane; i < gs; i += 32) {
+                const int c = g * gs + i;
+                xr[c] += yr[c] * f * w[c];
+                if (zero_y) yr[c] = 0.f;
+            }
+        }
+        return;
+    }
     for (int g = 0; g < groups; ++g) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = yr[g * gs + i]; ss = fmaf(v, v, ss); }
@@ -1117,7 +1133,11 @@ GG_API gg_group_rmsnorm_add(float* x, float* y, const float* w, int rows, int H,
                             cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H <= 0 || groups <= 0 || H % groups) return GG_ERR_ARG;
-    gg_launch(group_rmsnorm_add_kernel, dim3(rows), dim3(256), 0, stream, 1, x, y, w, H, groups, eps, zero_y);
+    // few rows (decode steps) of few runs: no more warps than runs, so that a block is not mostly idle
+    const int gs = H / groups;
+    int threads = 256;
+    if (gs <= 4096 && groups < 8) threads = 32 * groups;
+    gg_launch(group_rmsnorm_add_kernel, dim3(rows), dim3(threads), 0, stream, 1, x, y, w, H, groups, eps, zero_y);
     return gg_last_error();
 }
 

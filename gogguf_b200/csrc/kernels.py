@@ -641,10 +641,15 @@ def scan_finish(raw: torch.Tensor, x: Optional[torch.Tensor], g_off: int, out: t
         _p(seq_of_token), int(n_tokens), int(heads), int(dv), float(eps), float(out_scale), int(whole), int(gate), _stream())
 
 
+def stepsize_scan_scratch(n_tokens: int, n_seqs: int, heads: int, d: int, dv: int, chunk: int) -> int:
+    """Floats of scratch the chunked form of `stepsize_scan` needs: a state and a decay per chunk and head."""
+    return (n_tokens // chunk + n_seqs) * heads * (d * dv + 1)
+
+
 def stepsize_scan(xc: torch.Tensor, b_off: int, c_off: int, xd: torch.Tensor, dt_off: int, raw: torch.Tensor,
                   state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor,
                   dt_bias: torch.Tensor, neg_a: torch.Tensor, n_tokens: int, n_seqs: int, heads: int, groups: int, d: int,
-                  dv: int) -> None:
+                  dv: int, chunk: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
     """S_t = g_t S_(t-1) + (dt B_t) v_t^T, o_t = S_t^T C_t per head with dt = softplus(x_dt + dt_bias), g = exp(neg_a
     dt), from and into state [slots, heads, d, dv] (float32); raw [T, heads * dv] (float32) gets o_t.  xc [T, .]
     float32 holds v heads at column 0, B [groups, d] at b_off, C at c_off; xd [T, .] (compute dtype) x_dt at dt_off."""
@@ -656,10 +661,15 @@ def stepsize_scan(xc: torch.Tensor, b_off: int, c_off: int, xd: torch.Tensor, dt
         raise KernelError("stepsize_scan: xc is float32 and rows are contiguous")
     if tuple(state.shape[1:]) != (heads, d, dv) or raw.shape[-1] != heads * dv or dt_bias.numel() != heads or neg_a.numel() != heads:
         raise KernelError("stepsize_scan: the state must be [slots, heads, d, dv], raw [T, heads * dv], constants [heads]")
+    if chunk:
+        # prompts: what every chunk of `chunk` rows adds to the state, a walk over the chunks, the outputs chunk by chunk
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < stepsize_scan_scratch(n_tokens, n_seqs, heads, d, dv, chunk):
+            raise KernelError("stepsize_scan: the scratch is too small")
     kernel("recurrence", "gg_stepsize_scan")(
         _p(xc), xc.stride(0), int(b_off), int(c_off), _p(xd), dtype_code(xd.dtype), xd.stride(0), int(dt_off), _p(raw),
         _p(state), _p(cu_seqlens), _p(slots), _p(seq_of_token), _p(dt_bias), _p(neg_a), int(n_tokens), int(n_seqs),
-        int(heads), int(groups), int(d), int(dv), _stream())
+        int(heads), int(groups), int(d), int(dv), int(chunk), _p(scratch), _stream())
 
 
 def stepsize_finish(raw: torch.Tensor, xc: torch.Tensor, xd: torch.Tensor, z_off: int, skip: torch.Tensor,
@@ -709,6 +719,36 @@ def diag_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, ybias: Optional
     kernel("diag_recurrence", "gg_diag_scan")(_p(a), _p(b), _p(y), y.stride(0), dtype_code(y.dtype), _p(ybias), _p(out),
                                                _p(state), _p(cu_seqlens), _p(slots), _p(seq_of_token), int(n_tokens),
                                                int(n_seqs), C, _stream())
+
+
+DIAG_CHUNK = 64               # rows per chunk of the many-thread form (DG_CHUNK in csrc/diag_recurrence.cu)
+
+
+def diag_scan_chunks_scratch(n_tokens: int, n_seqs: int, C: int) -> int:
+    """Floats of scratch `diag_scan_chunks` needs: two numbers per chunk and channel."""
+    return (n_tokens // DIAG_CHUNK + n_seqs) * 2 * C
+
+
+def diag_scan_chunks(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, ybias: Optional[torch.Tensor], out: torch.Tensor,
+                     scratch: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor,
+                     seq_of_token: torch.Tensor, n_tokens: int, n_seqs: int) -> None:
+    """`diag_scan` for prompts, cut so that every chunk of 64 rows of every channel is a thread of its own: the
+    chunks' products and sums, a walk over a sequence's chunks, the rows again from each chunk's starting state."""
+    _need(a, torch.float32, "a")
+    _need(b, torch.float32, "b")
+    _need(state, torch.float32, "state")
+    _need(scratch, torch.float32, "scratch")
+    C = a.shape[-1]
+    if y.dtype != out.dtype or y.stride(-1) != 1 or y.shape[-1] != C or not out.is_contiguous() or out.shape[-1] != C \
+            or state.shape[-1] != C:
+        raise KernelError("diag_scan: shapes disagree")
+    if scratch.numel() < diag_scan_chunks_scratch(n_tokens, n_seqs, C):
+        raise KernelError("diag_scan: the scratch is too small")
+    if ybias is not None:
+        _need(ybias, torch.float32, "ybias")
+    kernel("diag_recurrence", "gg_diag_scan_chunks")(_p(a), _p(b), _p(y), y.stride(0), dtype_code(y.dtype), _p(ybias),
+                                                      _p(out), _p(scratch), _p(state), _p(cu_seqlens), _p(slots),
+                                                      _p(seq_of_token), int(n_tokens), int(n_seqs), C, _stream())
 
 
 # ------------------------------------------------------------------------------- routed experts

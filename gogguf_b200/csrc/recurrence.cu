@@ -672,11 +672,32 @@ template <typename T, int RPT>
 __global__ void __launch_bounds__(256) stepsize_scan_kernel(
     const float* xc, long long ldc, int b_off, int c_off, const T* xd, long long ldd, int dt_off, float* raw, float* state,
     const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ seq_of_token,
-    const float* __restrict__ dt_bias, const float* __restrict__ neg_a, int H, int d, int dv, int parts, int hpg) {
+    const float* __restrict__ dt_bias, const float* __restrict__ neg_a, int H, int d, int dv, int parts, int hpg,
+    int phase, int chunk, int n_seqs, float* chunk_state, float* chunk_decay) {
     pdl_launch();
     pdl_wait();
     extern __shared__ float sm[];
-    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * REC_COLS;
+    const int h = blockIdx.y, j0 = blockIdx.z * REC_COLS;
+    // phase 0: blockIdx.x is a sequence, walked whole from the slot's state and into it.  Phases 1 and 2: blockIdx.x
+    // is a chunk of `chunk` rows of some sequence (the chunks of the step in order, never across sequences); phase 1
+    // starts from zero and leaves what the chunk adds to the state and the product of its gates, phase 2 starts
+    // from the state the walk between the two left for the chunk and makes the outputs.
+    int b = blockIdx.x, start, end;
+    if (phase == 0) {
+        start = cu_seqlens[b];
+        end = cu_seqlens[b + 1];
+    } else {
+        int k = blockIdx.x;
+        bool found = false;
+        for (b = 0; b < n_seqs; ++b) {
+            const int s0 = cu_seqlens[b], n = cu_seqlens[b + 1] - s0;
+            const int nc = (n + chunk - 1) / chunk;
+            if (k < nc) { start = s0 + k * chunk; end = min(start + chunk, s0 + n); found = true; break; }
+            k -= nc;
+        }
+        if (!found) return;
+    }
+    const bool emit = phase != 1;
     const int ncols = min(REC_COLS, dv - j0);
     const int dp = parts * RPT;
     float* qs = sm;                             // [REC_TB][dp]  C_t
@@ -685,12 +706,12 @@ __global__ void __launch_bounds__(256) stepsize_scan_kernel(
     float* os = vs + REC_TB * REC_COLS;         // [REC_TB][parts][REC_COLS]
     float* dts = os + REC_TB * parts * REC_COLS;  // [REC_TB] dt
     float* gs = dts + REC_TB;                   // [REC_TB] g
-    const int start = cu_seqlens[b], end = cu_seqlens[b + 1];
     if (end <= start) return;
     const size_t HV = (size_t)H * dv;
     if (seq_of_token[start] < 0) {
-        for (int t = start; t < end; ++t)
-            for (int j = threadIdx.x; j < ncols; j += blockDim.x) raw[(size_t)t * HV + h * dv + j0 + j] = 0.f;
+        if (emit)
+            for (int t = start; t < end; ++t)
+                for (int j = threadIdx.x; j < ncols; j += blockDim.x) raw[(size_t)t * HV + h * dv + j0 + j] = 0.f;
         return;
     }
     const int part = threadIdx.x / REC_COLS, j = threadIdx.x - part * REC_COLS;
@@ -698,16 +719,18 @@ __global__ void __launch_bounds__(256) stepsize_scan_kernel(
     const int r0 = part * RPT;
     const int grp = h / hpg;
     const float bias = dt_bias[h], na = neg_a[h];
-    float* sp = state + (((size_t)slots[b] * H + h) * d) * dv + j0 + j;
+    float* sp = (phase == 0 ? state + (((size_t)slots[b] * H + h) * d) * dv
+                            : chunk_state + (((size_t)blockIdx.x * H + h) * d) * dv) + j0 + j;
     float S[RPT];
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) S[i] = (live && r0 + i < d) ? sp[(size_t)(r0 + i) * dv] : 0.f;
+    for (int i = 0; i < RPT; ++i) S[i] = (phase != 1 && live && r0 + i < d) ? sp[(size_t)(r0 + i) * dv] : 0.f;
     if (dp > d)
         for (int idx = threadIdx.x; idx < REC_TB * (dp - d); idx += blockDim.x) {
             const int tt = idx / (dp - d), i = d + idx % (dp - d);
             qs[tt * dp + i] = 0.f;
             ks[tt * dp + i] = 0.f;
         }
+    float gprod = 1.f;                          // (thread 0, phase 1) the product of the chunk's gates
     for (int t0 = start; t0 < end; t0 += REC_TB) {
         const int nb = min(REC_TB, end - t0);
         if (threadIdx.x < nb) {
@@ -716,6 +739,8 @@ __global__ void __launch_bounds__(256) stepsize_scan_kernel(
             gs[threadIdx.x] = expf(na * dt);
         }
         __syncthreads();
+        if (phase == 1 && threadIdx.x == 0)
+            for (int tt = 0; tt < nb; ++tt) gprod *= gs[tt];
         for (int idx = threadIdx.x; idx < nb * d; idx += blockDim.x) {
             const int tt = idx / d, i = idx - tt * d;
             const float* row = xc + (size_t)(t0 + tt) * ldc;
@@ -738,34 +763,69 @@ __global__ void __launch_bounds__(256) stepsize_scan_kernel(
                 for (int i = 0; i < RPT; i += 2) {
                     S[i] = fmaf(g, S[i], kt[i] * vj);
                     S[i + 1] = fmaf(g, S[i + 1], kt[i + 1] * vj);
-                    o0 = fmaf(S[i], qt[i], o0);
-                    o1 = fmaf(S[i + 1], qt[i + 1], o1);
+                    if (emit) {
+                        o0 = fmaf(S[i], qt[i], o0);
+                        o1 = fmaf(S[i + 1], qt[i + 1], o1);
+                    }
                 }
-                os[(tt * parts + part) * REC_COLS + j] = o0 + o1;
+                if (emit) os[(tt * parts + part) * REC_COLS + j] = o0 + o1;
             }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nb * ncols; idx += blockDim.x) {
-            const int tt = idx / ncols, c = idx - tt * ncols;
-            float o = 0.f;
-            for (int p = 0; p < parts; ++p) o += os[(tt * parts + p) * REC_COLS + c];
-            raw[(size_t)(t0 + tt) * HV + h * dv + j0 + c] = o;
-        }
+        if (emit)
+            for (int idx = threadIdx.x; idx < nb * ncols; idx += blockDim.x) {
+                const int tt = idx / ncols, c = idx - tt * ncols;
+                float o = 0.f;
+                for (int p = 0; p < parts; ++p) o += os[(tt * parts + p) * REC_COLS + c];
+                raw[(size_t)(t0 + tt) * HV + h * dv + j0 + c] = o;
+            }
         // (the next round writes dts / gs before its first barrier: every thread has read gs in the loop above, which
         // ends before the barrier that precedes these stores)
     }
+    if (phase == 2) return;
 #pragma unroll
     for (int i = 0; i < RPT; ++i)
         if (live && r0 + i < d) sp[(size_t)(r0 + i) * dv] = S[i];
+    if (phase == 1 && threadIdx.x == 0 && blockIdx.z == 0) chunk_decay[(size_t)blockIdx.x * H + h] = gprod;
+}
+
+// The walk between the two chunked phases: along a sequence's chunks S_in(c + 1) = D_c S_in(c) + U_c, from the slot's
+// state and into it; every chunk's U is replaced by its S_in.  grid (sequence, head, ceil(d dv / 256)).
+__global__ void __launch_bounds__(256) stepsize_chunk_walk_kernel(float* chunk_state, const float* chunk_decay, float* state,
+                                                                  const int* __restrict__ cu_seqlens,
+                                                                  const int* __restrict__ slots,
+                                                                  const int* __restrict__ seq_of_token, int H, int ddv,
+                                                                  int chunk) {
+    pdl_launch();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int start = cu_seqlens[s], end = cu_seqlens[s + 1];
+    if (e >= ddv || end <= start || seq_of_token[start] < 0) return;
+    int k0 = 0;
+    for (int b = 0; b < s; ++b) k0 += (cu_seqlens[b + 1] - cu_seqlens[b] + chunk - 1) / chunk;
+    const int nc = (end - start + chunk - 1) / chunk;
+    float* sp = state + ((size_t)slots[s] * H + h) * ddv + e;
+    float S = *sp;
+    for (int k = k0; k < k0 + nc; ++k) {
+        float* u = chunk_state + ((size_t)k * H + h) * ddv + e;
+        const float U = *u;
+        *u = S;
+        S = fmaf(chunk_decay[(size_t)k * H + h], S, U);
+    }
+    *sp = S;
 }
 
 // xc [T, ldc] float32; xd [T, ldd] in `dtype`; raw [T, H dv] float32; state [slots][H][d][dv] float32;
 // dt_bias, neg_a [H]; groups divides H.
+// chunk > 0 (prompts): the three-launch form over chunks of that many rows, with scratch of
+// (ntok / chunk + n_seqs) * H * (d * dv + 1) floats; chunk == 0: every sequence walked whole by its own CTAs.
 GG_API gg_stepsize_scan(const float* xc, long long ldc, int b_off, int c_off, const void* xd, int dtype, long long ldd,
                         int dt_off, float* raw, float* state, const int* cu_seqlens, const int* slots,
                         const int* seq_of_token, const float* dt_bias, const float* neg_a, int ntok, int n_seqs, int H,
-                        int groups, int d, int dv, cudaStream_t stream) {
+                        int groups, int d, int dv, int chunk, float* scratch, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (chunk < 0 || (chunk > 0 && scratch == nullptr)) return GG_ERR_ARG;
     if (H <= 0 || H > 65535 || groups <= 0 || H % groups || d <= 0 || d > 256 || dv <= 0 || raw == nullptr ||
         state == nullptr || dt_bias == nullptr || neg_a == nullptr)
         return GG_ERR_ARG;
@@ -779,9 +839,23 @@ GG_API gg_stepsize_scan(const float* xc, long long ldc, int b_off, int c_off, co
     do {                                                                                                             \
         if (smem > 48 * 1024)                                                                                        \
             cudaFuncSetAttribute(stepsize_scan_kernel<T_, R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        gg_launch(stepsize_scan_kernel<T_, R_>, dim3(n_seqs, H, tiles), dim3(parts * REC_COLS), smem, stream, 1, xc, ldc, \
-                  b_off, c_off, (const T_*)xd, ldd, dt_off, raw, state, cu_seqlens, slots, seq_of_token, dt_bias, neg_a, \
-                  H, d, dv, parts, H / groups);                                                                      \
+        if (chunk == 0) {                                                                                            \
+            gg_launch(stepsize_scan_kernel<T_, R_>, dim3(n_seqs, H, tiles), dim3(parts * REC_COLS), smem, stream, 1, xc, ldc, \
+                      b_off, c_off, (const T_*)xd, ldd, dt_off, raw, state, cu_seqlens, slots, seq_of_token, dt_bias, neg_a, \
+                      H, d, dv, parts, H / groups, 0, 0, n_seqs, (float*)nullptr, (float*)nullptr);                  \
+        } else {                                                                                                     \
+            const int chunks = ntok / chunk + n_seqs;                                                                \
+            float* cs = scratch;                                                                                     \
+            float* cd = scratch + (size_t)chunks * H * d * dv;                                                       \
+            gg_launch(stepsize_scan_kernel<T_, R_>, dim3(chunks, H, tiles), dim3(parts * REC_COLS), smem, stream, 1, xc, ldc, \
+                      b_off, c_off, (const T_*)xd, ldd, dt_off, raw, state, cu_seqlens, slots, seq_of_token, dt_bias, neg_a, \
+                      H, d, dv, parts, H / groups, 1, chunk, n_seqs, cs, cd);                                        \
+            gg_launch(stepsize_chunk_walk_kernel, dim3(n_seqs, H, (d * dv + 255) / 256), dim3(256), 0, stream, 1, cs,   \
+                      (const float*)cd, state, cu_seqlens, slots, seq_of_token, H, d * dv, chunk);                   \
+            gg_launch(stepsize_scan_kernel<T_, R_>, dim3(chunks, H, tiles), dim3(parts * REC_COLS), smem, stream, 1, xc, ldc, \
+                      b_off, c_off, (const T_*)xd, ldd, dt_off, raw, state, cu_seqlens, slots, seq_of_token, dt_bias, neg_a, \
+                      H, d, dv, parts, H / groups, 2, chunk, n_seqs, cs, cd);                                        \
+        }                                                                                                            \
     } while (0)
     GG_DISPATCH_DTYPE(dtype, T, if (rpt == 16) GG_SSCAN(T, 16); else GG_SSCAN(T, 32));
 #undef GG_SSCAN

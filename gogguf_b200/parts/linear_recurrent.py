@@ -34,6 +34,10 @@ from .base import Linear, Runtime, StepContext
 from .registry import register_mixer
 
 
+CHUNKED_FROM = 128      # new tokens of one sequence from which a step takes the recurrences' chunked forms
+SCAN_CHUNK = 64         # rows per chunk of the matrix-state recurrence's chunked form
+
+
 def _states(cache, what: str):
     if not isinstance(cache, tuple) or len(cache) != 2:
         raise ValueError(f"{what}: the convolution's state and the recurrence's state are expected")
@@ -106,7 +110,13 @@ class RGLRUMixer:
         b = ctx.ws.get("rglru_b", (T, C), torch.float32)
         K.rglru_gates(u, self.wa, self.wi, self.ba, self.bi, self.c, a, b, ctx.seq_of_token, T)
         out = ctx.ws.get("rglru_out", (T, C), self.rt.dtype)
-        K.diag_scan(a, b, p[:, :C], self.y_bias, out, st.state, ctx.cu_seqlens, ctx.slots, ctx.seq_of_token, T, ctx.n_seqs)
+        if ctx.max_new >= CHUNKED_FROM:
+            # prompts: chunks of rows over many threads (the same sums in another bracketing)
+            sums = ctx.ws.get("rglru_chunk_sums", (K.diag_scan_chunks_scratch(T, ctx.n_seqs, C),), torch.float32)
+            K.diag_scan_chunks(a, b, p[:, :C], self.y_bias, out, sums, st.state, ctx.cu_seqlens, ctx.slots, ctx.seq_of_token,
+                               T, ctx.n_seqs)
+        else:
+            K.diag_scan(a, b, p[:, :C], self.y_bias, out, st.state, ctx.cu_seqlens, ctx.slots, ctx.seq_of_token, T, ctx.n_seqs)
         self.o(out, residual, accumulate=True, ws=ctx.ws)
 
 
@@ -176,8 +186,13 @@ class Mamba2Mixer:
                       tail.state if tail is not None else None, ctx.cu_seqlens, ctx.slots, ctx.seq_of_token, T, ctx.n_seqs,
                       act=1, max_new=int(ctx.max_new))
         raw = ctx.ws.get("mamba2_raw", (T, inner), torch.float32)
+        chunk, scratch = 0, None
+        if ctx.max_new >= CHUNKED_FROM:
+            # prompts: chunks of rows over many CTAs (the same sums in another bracketing)
+            chunk = SCAN_CHUNK
+            scratch = ctx.ws.get("mamba2_chunk_states", (K.stepsize_scan_scratch(T, ctx.n_seqs, H, N, P, chunk),), torch.float32)
         K.stepsize_scan(xc, inner, inner + G * N, p, inner + self.conv_ch, raw, st.state, ctx.cu_seqlens, ctx.slots,
-                        ctx.seq_of_token, self.dt_bias, self.neg_a, T, ctx.n_seqs, H, G, N, P)
+                        ctx.seq_of_token, self.dt_bias, self.neg_a, T, ctx.n_seqs, H, G, N, P, chunk=chunk, scratch=scratch)
         y = ctx.ws.get("mamba2_out", (T, inner), self.rt.dtype)
         K.stepsize_finish(raw, xc, p, 0, self.skip, self.norm_weight, y, ctx.seq_of_token, T, H, P, self.norm_groups, self.eps)
         self.o(y, residual, accumulate=True, ws=ctx.ws)

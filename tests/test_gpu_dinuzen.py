@@ -203,6 +203,50 @@ def test_differential_attention_on_the_tensor_cores_against_the_plain_kernel(H, 
     assert float(o[1].abs().max()) == 0.0 and float(o[0].abs().max()) > 0.0
 
 
+@pytest.mark.parametrize("C,lens", [(60, (200, 1, 64, 65)), (512, (129,)), (24, (63, 300))])
+def test_vector_state_recurrence_in_chunks_against_row_by_row(C, lens):
+    K = _K()
+    g = _gen(C)
+    T = sum(lens)
+    cu, sot, _ = _batch(lens)
+    slots = _i32([2, 0, 5, 3][:len(lens)])
+    a = torch.rand(T, C, generator=g).pow(0.05).to(DEV)              # decays next to one: the state lives long
+    b = torch.randn(T, C, generator=g).to(DEV)
+    y = torch.randn(T, C + 8, generator=g).to(DEV)
+    yb = torch.randn(C, generator=g).to(DEV)
+    st0 = torch.randn(6, C, generator=g).to(DEV)
+    st1, st2 = st0.clone(), st0.clone()
+    o1, o2 = torch.empty(T, C, device=DEV), torch.empty(T, C, device=DEV)
+    K.diag_scan(a, b, y[:, :C], yb, o1, st1, cu, slots, sot, T, len(lens))
+    scratch = torch.empty(K.diag_scan_chunks_scratch(T, len(lens), C), device=DEV)
+    K.diag_scan_chunks(a, b, y[:, :C], yb, o2, scratch, st2, cu, slots, sot, T, len(lens))
+    assert rel_err(o2, o1) < 1e-5 and rel_err(st2, st1) < 1e-5
+    assert torch.equal(st2[1], st0[1]) and torch.equal(st2[4], st0[4])          # other slots untouched
+
+
+@pytest.mark.parametrize("H,G,N,P,lens", [(3, 3, 20, 24, (200, 1, 64, 65)), (4, 2, 128, 64, (129,)), (2, 1, 72, 40, (63, 300))])
+def test_matrix_state_recurrence_with_step_sizes_in_chunks_against_row_by_row(H, G, N, P, lens):
+    K = _K()
+    g = _gen(H * N + P)
+    T = sum(lens)
+    cu, sot, _ = _batch(lens)
+    slots = _i32([2, 0, 5, 3][:len(lens)])
+    inner = H * P
+    xc = torch.randn(T, inner + 2 * G * N, generator=g).to(DEV)
+    xd = (torch.randn(T, H + 4, generator=g) - 2.0).to(DEV)          # small step sizes: slow decays
+    dt_bias = torch.randn(H, generator=g).to(DEV) * 0.3
+    neg_a = -torch.rand(H, generator=g).to(DEV)
+    st0 = torch.randn(6, H, N, P, generator=g).to(DEV)
+    st1, st2 = st0.clone(), st0.clone()
+    r1, r2 = torch.empty(T, inner, device=DEV), torch.empty(T, inner, device=DEV)
+    K.stepsize_scan(xc, inner, inner + G * N, xd, 4, r1, st1, cu, slots, sot, dt_bias, neg_a, T, len(lens), H, G, N, P)
+    scratch = torch.empty(K.stepsize_scan_scratch(T, len(lens), H, N, P, 64), device=DEV)
+    K.stepsize_scan(xc, inner, inner + G * N, xd, 4, r2, st2, cu, slots, sot, dt_bias, neg_a, T, len(lens), H, G, N, P,
+                    chunk=64, scratch=scratch)
+    assert rel_err(r2, r1) < 1e-5 and rel_err(st2, st1) < 1e-5
+    assert torch.equal(st2[1], st0[1]) and torch.equal(st2[4], st0[4])
+
+
 def _one_layer(kind, mixer, mlp=None, width=64, groups=2, vocab=61, eps=1e-5):
     return model(vocab, width, eps, groups, [layer(kind, mixer, mlp)])
 
