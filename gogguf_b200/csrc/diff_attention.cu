@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* out, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens, const int* __restrict__ page_table,
     int max_pages, int n_seqs, int H, int G, int hpg, int tpt, float scale, float cap, int window, float lambda,
-    float eps, float out_scale, const PageBounds pb) {
+    float eps, float out_scale, int nsplit, float* partial, const PageBounds pb) {
     pdl_wait();
     constexpr int QS = 2 * D + 8, KS = 2 * D + 8, VS = DV + 8;     // row strides in elements (16 bytes of padding)
     extern __shared__ __align__(16) unsigned char da_smem[];
@@ -306,6 +306,7 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     const int nrows = ntok * hpg;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (seq_of_token[t0] < 0) {                                     // padding rows of a replayed batch: zeros
+        if (nsplit > 1) return;                                     // (the kernel that merges the shares writes them)
         for (int idx = threadIdx.x; idx < nrows * DV; idx += blockDim.x) {
             const int r = idx / DV, c = idx - r * DV;
             out[((size_t)(t0 + r / hpg) * H + g * hpg + r % hpg) * DV + c] = __float2bfloat16_rn(0.f);
@@ -323,7 +324,12 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     const int pos0 = positions[t0];
     const int pos_last = pos0 + ntok - 1;
     const int lo_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int j_lo = lo_key / DA_KEYS, j_hi = pos_last / DA_KEYS;
+    int j_lo = lo_key / DA_KEYS, j_hi = pos_last / DA_KEYS;
+    if (nsplit > 1) {                                               // this CTA's share of the tiles (it may be empty)
+        const int per = (j_hi - j_lo + nsplit) / nsplit;
+        j_lo += (int)blockIdx.z * per;
+        j_hi = min(j_hi, j_lo + per - 1);
+    }
     const int* pt = page_table + (size_t)b * max_pages;
 
     auto load_tile = [&](int j, int stage) {
@@ -361,7 +367,7 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     }
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
-    load_tile(j_lo, 0);
+    if (j_lo <= j_hi) load_tile(j_lo, 0);
     for (int j = j_lo; j <= j_hi; ++j) {
         const int stage = (j - j_lo) & 1;
         if (j < j_hi) {
@@ -451,6 +457,25 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     // the difference of the maps, its root mean square over the head's values, the store
     const float l1A = da_quad_sum(lrun[0][0]), l1B = da_quad_sum(lrun[0][1]);
     const float l2A = da_quad_sum(lrun[1][0]), l2B = da_quad_sum(lrun[1][1]);
+    if (nsplit > 1) {
+        // a share of the keys: each row's running maximum, sum and weighted values per map go to scratch
+        // [row of the step][head][share][map][2 + DV]; diff_attention_merge_kernel puts the shares together
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = half ? rB : rA;
+            if ((half ? posB : posA) < 0) continue;
+            float* base = partial + (((size_t)(t0 + r / hpg) * H + g * hpg + r % hpg) * nsplit + blockIdx.z) * 2 * (2 + DV);
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                float* pm = base + m * (2 + DV);
+                if (t4 == 0) { pm[0] = mrun[m][half]; pm[1] = half ? (m ? l2B : l1B) : (m ? l2A : l1A); }
+#pragma unroll
+                for (int n = 0; n < DV / 8; ++n)
+                    *reinterpret_cast<float2*>(pm + 2 + n * 8 + 2 * t4) = make_float2(O[m][n][2 * half], O[m][n][2 * half + 1]);
+            }
+        }
+        return;
+    }
     const float i1A = posA >= 0 ? 1.0f / l1A : 0.f, i1B = posB >= 0 ? 1.0f / l1B : 0.f;
     const float i2A = posA >= 0 ? lambda / l2A : 0.f, i2B = posB >= 0 ? lambda / l2B : 0.f;
     float ssA = 0.f, ssB = 0.f;
@@ -480,20 +505,62 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     }
 }
 
+// One block per (row of the step, head): the shares' maxima, sums and weighted values per map are put together, then
+// out = out_scale * unit(a1 - lambda a2) as in the kernels above.  partial [T][H][nsplit][2][2 + dv] float32.
+__global__ void __launch_bounds__(128) diff_attention_merge_kernel(const float* partial, bf16* out,
+                                                                   const int* __restrict__ seq_of_token, int H, int dv,
+                                                                   int nsplit, float lambda, float eps, float out_scale) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const int t = blockIdx.x, h = blockIdx.y;
+    bf16* o = out + ((size_t)t * H + h) * dv;
+    if (seq_of_token[t] < 0) {
+        for (int i = threadIdx.x; i < dv; i += blockDim.x) o[i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const float* base = partial + ((size_t)t * H + h) * nsplit * 2 * (2 + dv);
+    float M[2] = {-INFINITY, -INFINITY}, L[2] = {0.f, 0.f};
+    for (int m = 0; m < 2; ++m) {
+        for (int z = 0; z < nsplit; ++z) M[m] = fmaxf(M[m], base[(z * 2 + m) * (2 + dv)]);
+        for (int z = 0; z < nsplit; ++z) {
+            const float mz = base[(z * 2 + m) * (2 + dv)];
+            if (mz != -INFINITY) L[m] += base[(z * 2 + m) * (2 + dv) + 1] * expf(mz - M[m]);
+        }
+    }
+    // (dv <= 128 = the block: a thread owns one value)
+    const int i = threadIdx.x;
+    float df = 0.f;
+    if (i < dv) {
+        float a[2] = {0.f, 0.f};
+        for (int m = 0; m < 2; ++m)
+            for (int z = 0; z < nsplit; ++z) {
+                const float mz = base[(z * 2 + m) * (2 + dv)];
+                if (mz != -INFINITY) a[m] += base[(z * 2 + m) * (2 + dv) + 2 + i] * expf(mz - M[m]);
+            }
+        df = a[0] / L[0] - lambda * a[1] / L[1];
+    }
+    const float ss = block_sum(df * df, red);
+    if (i < dv) o[i] = __float2bfloat16_rn(df * out_scale / sqrtf(ss / (float)dv + eps));
+}
+
 template <int D, int DV>
 static int da_mma_launch(const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* out, const int* positions,
                          const int* seq_of_token, const int* cu_seqlens, const int* page_table, int max_pages, int n_pages,
                          int ntok, int n_seqs, int H, int G, float scale, float cap, int window, float lambda, float eps,
-                         float out_scale, int* status, cudaStream_t stream) {
+                         float out_scale, int nsplit, float* partial, int* status, cudaStream_t stream) {
     const int hpg = H / G;
     const int tpt = DA_ROWS / hpg;
     const size_t smem = ((size_t)DA_ROWS * (2 * D + 8) + 2 * DA_KEYS * (2 * D + 8) + 2 * DA_KEYS * (DV + 8)) * sizeof(bf16);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(diff_attention_mma_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int tiles = (ntok + tpt - 1) / tpt + n_seqs;             // an upper bound on the sequences' tiles
-    return gg_launch(diff_attention_mma_kernel<D, DV>, dim3(tiles, G), dim3(128), smem, stream, 1, q, k_pool, v_pool, out,
-                     positions, seq_of_token, cu_seqlens, page_table, max_pages, n_seqs, H, G, hpg, tpt, scale, cap, window,
-                     lambda, eps, out_scale, PageBounds{n_pages, status});
+    const int rc = gg_launch(diff_attention_mma_kernel<D, DV>, dim3(tiles, G, nsplit), dim3(128), smem, stream, 1, q, k_pool,
+                             v_pool, out, positions, seq_of_token, cu_seqlens, page_table, max_pages, n_seqs, H, G, hpg, tpt,
+                             scale, cap, window, lambda, eps, out_scale, nsplit, partial, PageBounds{n_pages, status});
+    if (rc != 0 || nsplit <= 1) return rc;
+    return gg_launch(diff_attention_merge_kernel, dim3(ntok, H), dim3(128), 0, stream, 1, (const float*)partial, out,
+                     seq_of_token, H, DV, nsplit, lambda, eps, out_scale);
 }
 
 // 1 if the tensor-core form takes these sizes (bfloat16 only), else 0.
@@ -502,17 +569,20 @@ GG_API gg_diff_attention_mma_takes(int H, int G, int d, int dv, int page_size) {
     return (dims && page_size == DA_KEYS && G > 0 && H % G == 0 && H / G <= DA_ROWS && G <= 65535) ? 1 : 0;
 }
 
-// As gg_diff_attention for bfloat16 tensors, with the step's cu_seqlens [n_seqs + 1].
+// As gg_diff_attention for bfloat16 tensors, with the step's cu_seqlens [n_seqs + 1].  nsplit > 1 (steps of few
+// rows and long contexts): every (tile, kv head) is the work of nsplit CTAs, each with a share of the key tiles, and a
+// second kernel merges them; partial is scratch of ntok * H * nsplit * 2 * (2 + dv) floats.
 GG_API gg_diff_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
                              const int* seq_of_token, const int* cu_seqlens, const int* page_table, int max_pages,
                              int page_size, int n_pages, int ntok, int n_seqs, int H, int G, int d, int dv, float scale,
-                             float cap, int window, float lambda, float eps, float out_scale, int* status,
-                             cudaStream_t stream) {
+                             float cap, int window, float lambda, float eps, float out_scale, int nsplit, float* partial,
+                             int* status, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (!gg_diff_attention_mma_takes(H, G, d, dv, page_size)) return GG_ERR_ARG;
+    if (nsplit < 1 || nsplit > 64 || (nsplit > 1 && partial == nullptr)) return GG_ERR_ARG;
 #define DA_GO(D_, V_) return da_mma_launch<D_, V_>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, positions, \
         seq_of_token, cu_seqlens, page_table, max_pages, n_pages, ntok, n_seqs, H, G, scale, cap, window, lambda, eps,      \
-        out_scale, status, stream)
+        out_scale, nsplit, partial, status, stream)
     if (d == 32) { if (dv == 32) DA_GO(32, 32); if (dv == 64) DA_GO(32, 64); DA_GO(32, 128); }
     if (d == 64) { if (dv == 32) DA_GO(64, 32); if (dv == 64) DA_GO(64, 64); DA_GO(64, 128); }
     if (dv == 32) DA_GO(128, 32);

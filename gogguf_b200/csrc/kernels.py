@@ -428,9 +428,15 @@ def diff_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
                        positions: torch.Tensor, seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor,
                        page_table: torch.Tensor, page_size: int, n_tokens: int, n_seqs: int, heads: int, kv_heads: int,
                        d: int, dv: int, scale: float, cap: float, window: int, lam: float, eps: float,
-                       out_scale: float) -> None:
+                       out_scale: float, nsplit: int = 1, partial: Optional[torch.Tensor] = None) -> None:
     """`diff_attention` on the tensor cores (mma.sync) for bfloat16 tensors: the query heads of a kv head and up to
-    64 / (heads / kv_heads) consecutive tokens of a sequence share a CTA and every page they read."""
+    64 / (heads / kv_heads) consecutive tokens of a sequence share a CTA and every page they read.  nsplit > 1: the
+    key tiles of every such CTA are shared out over nsplit CTAs and merged by a second kernel (`partial`: float32
+    scratch of `diff_attention_partial_elems`)."""
+    if nsplit > 1:
+        _need(partial, torch.float32, "partial")
+        if partial.numel() < diff_attention_partial_elems(n_tokens, heads, dv, nsplit):
+            raise KernelError("diff_attention_mma: the scratch for the shares is too small")
     for t, n in ((q, "q"), (k_pool, "k_pool"), (v_pool, "v_pool"), (out, "out")):
         _need(t, torch.bfloat16, n)
     if k_pool.shape[-1] != 2 * d or v_pool.shape[-1] != dv or k_pool.shape[1] != kv_heads:
@@ -439,8 +445,23 @@ def diff_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     kernel("diff_attention", "gg_diff_attention_mma")(
         _p(q), _p(k_pool), _p(v_pool), _p(out), _p(positions), _p(seq_of_token), _p(cu_seqlens), _p(page_table),
         page_table.shape[-1], int(page_size), k_pool.shape[0], int(n_tokens), int(n_seqs), int(heads), int(kv_heads),
-        int(d), int(dv), float(scale), float(cap), int(window), float(lam), float(eps), float(out_scale),
-        _p(status_word(q.device)), _stream())
+        int(d), int(dv), float(scale), float(cap), int(window), float(lam), float(eps), float(out_scale), int(nsplit),
+        _p(partial), _p(status_word(q.device)), _stream())
+
+
+def diff_attention_partial_elems(n_tokens: int, heads: int, dv: int, nsplit: int) -> int:
+    return n_tokens * heads * nsplit * 2 * (2 + dv)
+
+
+def diff_attention_splits(n_tokens: int, n_seqs: int, heads: int, kv_heads: int, max_ctx: int) -> int:
+    """Into how many shares a step's key tiles are cut: none while the step's (tile, kv head) pairs fill the GPU or
+    the contexts are short, else towards two CTAs a multiprocessor, at least two tiles a share."""
+    tpt = max(1, 64 // (heads // kv_heads))
+    ctas = max(n_seqs, -(-n_tokens // tpt)) * kv_heads
+    tiles = -(-max_ctx // 64)
+    if ctas >= 148 or tiles < 4:
+        return 1
+    return int(max(1, min(32, 296 // max(ctas, 1), tiles // 2)))
 
 
 # ------------------------------------------------------------------------------- latent attention

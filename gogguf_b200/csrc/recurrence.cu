@@ -807,11 +807,20 @@ __global__ void __launch_bounds__(256) stepsize_chunk_walk_kernel(float* chunk_s
     const int nc = (end - start + chunk - 1) / chunk;
     float* sp = state + ((size_t)slots[s] * H + h) * ddv + e;
     float S = *sp;
-    for (int k = k0; k < k0 + nc; ++k) {
-        float* u = chunk_state + ((size_t)k * H + h) * ddv + e;
-        const float U = *u;
-        *u = S;
-        S = fmaf(chunk_decay[(size_t)k * H + h], S, U);
+    for (int k = k0; k < k0 + nc; k += 8) {              // eight chunks' loads in flight, then the chain
+        float U[8], D[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (k + i < k0 + nc) {
+                U[i] = chunk_state[((size_t)(k + i) * H + h) * ddv + e];
+                D[i] = chunk_decay[(size_t)(k + i) * H + h];
+            }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (k + i < k0 + nc) {
+                chunk_state[((size_t)(k + i) * H + h) * ddv + e] = S;
+                S = fmaf(D[i], S, U[i]);
+            }
     }
     *sp = S;
 }

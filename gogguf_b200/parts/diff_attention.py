@@ -135,9 +135,13 @@ class DiffAttentionMixer:
                        self.rot)
         o = ctx.ws.get("diff_attn_out", (T, H * dv), dt)
         if self._mma and K.diff_attention_mma_takes(H, G, d, dv, cache.page_size):
+            # steps of few rows over long contexts (decode steps): the key tiles are shared out over several CTAs
+            nsplit = K.diff_attention_splits(T, ctx.n_seqs, H, G, int(ctx.max_ctx)) if ctx.max_new <= 4 else 1
+            partial = (ctx.ws.get("diff_attn_shares", (K.diff_attention_partial_elems(T, H, dv, nsplit),), torch.float32)
+                       if nsplit > 1 else None)
             K.diff_attention_mma(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, ctx.cu_seqlens, table,
                                  cache.page_size, T, ctx.n_seqs, H, G, d, dv, self.scale, self.cap, self.window, self.lam,
-                                 self.eps, self.out_scale)
+                                 self.eps, self.out_scale, nsplit=nsplit, partial=partial)
         else:
             K.diff_attention(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, table, cache.page_size, T, H, G, d, dv,
                              self.scale, self.cap, self.window, self.lam, self.eps, self.out_scale)

@@ -190,6 +190,12 @@ def test_differential_attention_on_the_tensor_cores_against_the_plain_kernel(H, 
         b_ = torch.empty_like(a)
         K.diff_attention(q, kpool, vpool, a, pos, sot, table, ps, T, H, G, d, dv, 0.11, cap, window, 0.37, 1e-6, 0.8)
         K.diff_attention_mma(q, kpool, vpool, b_, pos, sot, cu, table, ps, T, 3, H, G, d, dv, 0.11, cap, window, 0.37, 1e-6, 0.8)
+        # the same with every CTA's key tiles shared out over three CTAs and merged by the second kernel
+        c_ = torch.empty_like(a)
+        shares = torch.empty(K.diff_attention_partial_elems(T, H, dv, 3), device=DEV)
+        K.diff_attention_mma(q, kpool, vpool, c_, pos, sot, cu, table, ps, T, 3, H, G, d, dv, 0.11, cap, window, 0.37, 1e-6, 0.8,
+                             nsplit=3, partial=shares)
+        assert float(((c_.float() - b_.float()).abs().max(dim=-1).values / a.float().abs().max()).max()) < 1.2e-2
         err = (a.float() - b_.float()).abs().max(dim=-1).values / a.float().abs().max()
         assert float(err.max()) < 3e-2 and float(err.median()) < 1e-2, (float(err.max()), float(err.median()), lens)   # (an output rounds to 2^-8 of itself)
         done = [x + n for x, n in zip(done, lens)]
