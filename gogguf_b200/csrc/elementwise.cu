@@ -1215,9 +1215,33 @@ __global__ void __launch_bounds__(256) depth_mix_kernel(float* hist, float* x, c
     x[i] = acc;
 }
 
+// The same with 16-byte accesses (n a multiple of four, buffers on 16-byte boundaries).
+__global__ void __launch_bounds__(256) depth_mix_vec_kernel(float4* hist, float4* x, const float* __restrict__ coeff,
+                                                            int store_at, int n_terms, long long n4) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 v = x[i];
+    hist[(size_t)store_at * n4 + i] = v;
+    if (n_terms <= 0) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < n_terms; ++j) {
+        const float cj = coeff[j];
+        const float4 hj = j == store_at ? v : hist[(size_t)j * n4 + i];
+        acc.x = fmaf(cj, hj.x, acc.x); acc.y = fmaf(cj, hj.y, acc.y); acc.z = fmaf(cj, hj.z, acc.z); acc.w = fmaf(cj, hj.w, acc.w);
+    }
+    x[i] = acc;
+}
+
 GG_API gg_depth_mix(float* hist, float* x, const float* coeff, int store_at, int n_terms, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (store_at < 0 || n_terms < 0 || (n_terms > 0 && coeff == nullptr)) return GG_ERR_ARG;
+    if ((n & 3) == 0 && (((uintptr_t)hist | (uintptr_t)x) & 15) == 0) {
+        gg_launch(depth_mix_vec_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream, 1, (float4*)hist, (float4*)x,
+                  coeff, store_at, n_terms, n / 4);
+        return gg_last_error();
+    }
     gg_launch(depth_mix_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, hist, x, coeff, store_at, n_terms, n);
     return gg_last_error();
 }
@@ -1361,6 +1385,83 @@ __global__ void __launch_bounds__(256) column_conv_state_kernel(const T* h, long
     }
 }
 
+// The same for up to eight taps, a thread walking TT consecutive rows of one channel with the window of earlier values
+// in registers, so that a row of h is read once instead of once per tap; the window is filled again (from the
+// step's rows or the sequence's state) where a new sequence starts among the rows.  Blocks (TT rows, 256 channels).
+template <typename T, int TAPS, int TT>
+__global__ void __launch_bounds__(256) column_conv_tile_kernel(const T* h, long long ldh, float* out, long long ldo,
+                                                               const float* __restrict__ w, const float* __restrict__ bias,
+                                                               const float* __restrict__ in_bias, float* state,
+                                                               const int* __restrict__ cu_seqlens,
+                                                               const int* __restrict__ slots,
+                                                               const int* __restrict__ seq_of_token, int C, int ntok, int act,
+                                                               int one_each) {
+    pdl_launch();
+    pdl_wait();
+    constexpr int R = TAPS - 1;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float wr[TAPS];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wr[j] = w[(size_t)j * C + c];
+    const float ob = bias != nullptr ? bias[c] : 0.f, ib = in_bias != nullptr ? in_bias[c] : 0.f;
+    float win[R > 0 ? R : 1];
+    const int t0 = blockIdx.x * TT;
+    int prev_b = -2;
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+        const int t = t0 + tt;
+        if (t >= ntok) break;
+        const int b = seq_of_token[t];
+        if (b < 0) { out[(size_t)t * ldo + c] = 0.f; prev_b = -2; continue; }
+        float* st = state + (size_t)slots[b] * R * C + c;
+        if (b != prev_b) {
+            const int start = cu_seqlens[b];
+#pragma unroll
+            for (int j = 0; j < R; ++j) {
+                const int s = t - R + j;
+                win[j] = s >= start ? to_f<T>(h[(size_t)s * ldh + c]) + ib : st[(size_t)(R + (s - start)) * C];
+            }
+            prev_b = b;
+        }
+        const float cur = to_f<T>(h[(size_t)t * ldh + c]) + ib;
+        float acc = fmaf(wr[R], cur, ob);
+#pragma unroll
+        for (int j = 0; j < R; ++j) acc = fmaf(wr[j], win[j], acc);
+        out[(size_t)t * ldo + c] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
+#pragma unroll
+        for (int j = 0; j + 1 < R; ++j) win[j] = win[j + 1];
+        if (R > 0) win[R - 1] = cur;
+        if (one_each) {                                   // the sequence's only row of the step: its state moves on
+#pragma unroll
+            for (int j = 0; j < R; ++j) st[(size_t)j * C] = win[j];
+        }
+    }
+}
+
+template <typename T, int TAPS>
+static int column_conv_tile_launch(const T* h, long long ldh, float* out, long long ldo, const float* w, const float* bias,
+                                   const float* in_bias, float* state, const int* cu_seqlens, const int* slots,
+                                   const int* seq_of_token, int ntok, int C, int act, int one_each, cudaStream_t stream) {
+    const unsigned cb = (unsigned)((C + 255) / 256);
+    if (ntok < 1024 || one_each)       // few rows, or a row a sequence: a row a thread, so that the step fills more of the GPU
+        return gg_launch(column_conv_tile_kernel<T, TAPS, 1>, dim3((unsigned)ntok, cb), dim3(256), 0, stream, 1, h, ldh, out, ldo,
+                         w, bias, in_bias, state, cu_seqlens, slots, seq_of_token, C, ntok, act, one_each);
+    return gg_launch(column_conv_tile_kernel<T, TAPS, 8>, dim3((unsigned)((ntok + 7) / 8), cb), dim3(256), 0, stream, 1, h, ldh,
+                     out, ldo, w, bias, in_bias, state, cu_seqlens, slots, seq_of_token, C, ntok, act, one_each);
+}
+
+template <typename T>
+static int column_conv_tile(int taps, const T* h, long long ldh, float* out, long long ldo, const float* w, const float* bias,
+                            const float* in_bias, float* state, const int* cu_seqlens, const int* slots,
+                            const int* seq_of_token, int ntok, int C, int act, int one_each, cudaStream_t stream) {
+#define CC_CASE(N) case N: return column_conv_tile_launch<T, N>(h, ldh, out, ldo, w, bias, in_bias, state, cu_seqlens, slots, \
+                                                                seq_of_token, ntok, C, act, one_each, stream);
+    switch (taps) { CC_CASE(1) CC_CASE(2) CC_CASE(3) CC_CASE(4) CC_CASE(5) CC_CASE(6) CC_CASE(7) CC_CASE(8) }
+#undef CC_CASE
+    return GG_ERR_ARG;
+}
+
 // w [taps][C] float32 (a tap's weights side by side); state [slots][taps - 1][C] float32 (null only for one tap).
 GG_API gg_column_conv(const void* h, long long ldh, int dtype, float* out, long long ldo, const float* w, const float* bias,
                       const float* in_bias, float* state, const int* cu_seqlens, const int* slots, const int* seq_of_token,
@@ -1371,8 +1472,13 @@ GG_API gg_column_conv(const void* h, long long ldh, int dtype, float* out, long 
     const int cb = min((C + 255) / 256, 65535);
     const int one_each = max_new == 1;
     GG_DISPATCH_DTYPE(dtype, T,
-        gg_launch(column_conv_kernel<T>, dim3(ntok, cb), dim3(256), 0, stream, 1, (const T*)h, ldh, out, ldo, w, bias, in_bias,
-                  state, cu_seqlens, slots, seq_of_token, C, taps, act, one_each);
+        if (taps <= 8 && cb <= 65535) {
+            column_conv_tile<T>(taps, (const T*)h, ldh, out, ldo, w, bias, in_bias, state, cu_seqlens, slots, seq_of_token, ntok,
+                                C, act, one_each, stream);
+        } else {
+            gg_launch(column_conv_kernel<T>, dim3(ntok, cb), dim3(256), 0, stream, 1, (const T*)h, ldh, out, ldo, w, bias, in_bias,
+                      state, cu_seqlens, slots, seq_of_token, C, taps, act, one_each);
+        }
         if (taps > 1 && !one_each)
             gg_launch(column_conv_state_kernel<T>, dim3(n_seqs, cb), dim3(256), 0, stream, 1, (const T*)h, ldh, in_bias, state,
                       cu_seqlens, slots, seq_of_token, C, taps));

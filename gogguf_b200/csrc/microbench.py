@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample|latent|retention|recurrence] [--m 1,8,64] [--ctx 2048,8192]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample|latent|retention|recurrence|dinuzen] [--m 1,8,64] [--ctx 2048,8192]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -412,9 +412,125 @@ def recurrence(sizes=((8, 128, 128, 2048), (16, 128, 128, 4096))) -> None:
         torch.cuda.empty_cache()
 
 
+def dinuzen(sizes=((16, 4, 64, 128, 2048, 32, 64, 128, 8), (32, 8, 128, 128, 4096, 64, 64, 128, 8))) -> None:
+    """The kernels the Dinuzen design added, at layer sizes (heads, kv heads, d, dv, width, state-space heads, their
+    value size, state size, groups): differential attention (csrc/diff_attention.cu) on a prompt of 2,048 tokens
+    against the bf16 tensor peak and in decode steps against the copy bandwidth; the two recurrences' prompt and
+    decode forms; the convolution of a projection's columns, the token shift, the norm in groups with its add, the
+    weighted sum over depth."""
+    from . import kernels as K
+    dev = "cuda:0"
+    hbm, tflops, src = _peaks()
+    props = torch.cuda.get_device_properties(0)
+    fp32_tflops = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
+    print(f"peaks ({src}): {hbm:.0f} GB/s copy, {tflops:.0f} TFLOP/s bf16; float32 multiply-add rate {fp32_tflops:.1f} TFLOP/s (nominal)")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    for H, G, d, dv, W, SH, SP, SN, SG in sizes:
+        T, ps = 2048, 64
+        # ---- differential attention: one prompt of T tokens
+        pages = T // ps
+        kpool = (torch.randn(pages * 64 + 1, G, ps, 2 * d, device=dev) * 0.3).to(torch.bfloat16)
+        vpool = torch.randn(pages * 64 + 1, G, ps, dv, device=dev).to(torch.bfloat16)
+        q = torch.randn(T, H * 2 * d, device=dev).to(torch.bfloat16)
+        o = torch.empty(T, H * dv, device=dev, dtype=torch.bfloat16)
+        pos, sot, cu = i32(list(range(T))), i32([0] * T), i32([0, T])
+        table = i32([list(range(pages))])
+        us = _time_graph(lambda i: K.diff_attention_mma(q, kpool, vpool, o, pos, sot, cu, table, ps, T, 1, H, G, d, dv, d ** -0.5,
+                                                        30.0, 0, 0.4, 1e-6, 0.7), reps=10)
+        flops = 2 * H * (2 * d + 2 * dv) * (T * (T + 1) // 2)
+        print(f"diff attention prompt  H={H} G={G} d={d} dv={dv} T={T}: {us:8.1f} us  {flops / us / 1e6:6.1f} TFLOP/s "
+              f"({flops / us / 1e6 / tflops:.3f} of the bf16 peak)", flush=True)
+        us = _time_graph(lambda i: K.diff_attention(q[:256], kpool, vpool, o[:256], pos[T - 256:], sot[:256], table, ps, 256, H, G, d,
+                                                    dv, d ** -0.5, 30.0, 0, 0.4, 1e-6, 0.7), reps=3)
+        print(f"   plain kernel, the last 256 rows of that prompt: {us:8.1f} us", flush=True)
+        # ---- decode steps over contexts of T tokens
+        for B in (8, 64):
+            tb = i32([[(b * pages + j) for j in range(pages)] for b in range(B)])
+            posb, sotb, cub = i32([T - 1] * B), i32(list(range(B))), i32(list(range(B + 1)))
+            ns = K.diff_attention_splits(B, B, H, G, T)
+            part = torch.empty(max(K.diff_attention_partial_elems(B, H, dv, ns), 1), device=dev)
+            us = _time_graph(lambda i: K.diff_attention_mma(q[:B], kpool, vpool, o[:B], posb, sotb, cub, tb, ps, B, B, H, G, d, dv,
+                                                            d ** -0.5, 30.0, 0, 0.4, 1e-6, 0.7, nsplit=ns, partial=part if ns > 1 else None))
+            nbytes = B * T * G * (2 * d + dv) * 2
+            print(f"diff attention decode  batch {B:2d} ctx {T} ({ns} shares): {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
+                  f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)
+        del kpool, vpool
+        # ---- the vector-state recurrence (width W)
+        a = torch.rand(T, W, device=dev).pow(0.05)
+        b = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(torch.bfloat16)
+        outw = torch.empty(T, W, device=dev, dtype=torch.bfloat16)
+        st = torch.zeros(64, W, device=dev)
+        zero = i32([0])
+        sums = torch.empty(K.diag_scan_chunks_scratch(T, 1, W), device=dev)
+        us = _time_graph(lambda i: K.diag_scan_chunks(a, b, y, None, outw, sums, st, cu, zero, sot, T, 1), reps=10)
+        nbytes = T * W * (2 * 8 + 2 + 2)
+        print(f"vector scan prompt  W={W} T={T} (chunks): {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s ({nbytes / us / 1e3 / hbm:.2f})", flush=True)
+        us = _time_graph(lambda i: K.diag_scan(a, b, y, None, outw, st, cu, zero, sot, T, 1), reps=3)
+        print(f"   row by row: {us:8.1f} us", flush=True)
+        nb = W // 16
+        wa = torch.randn(16, nb, nb, device=dev) * 0.05
+        u = torch.randn(T, W, device=dev)
+        bz, cz = torch.zeros(W, device=dev), -torch.rand(W, device=dev)
+        us = _time_graph(lambda i: K.rglru_gates(u, wa, wa, bz, bz, cz, a, b, sot, T), reps=10)
+        flops = 2 * T * 2 * W * nb
+        print(f"gates of the unit   W={W} 16 blocks T={T}: {us:8.1f} us  {flops / us / 1e6:6.2f} TFLOP/s ({flops / us / 1e6 / fp32_tflops:.2f} of the float32 rate)", flush=True)
+        for B in (8, 64):
+            sotb, cub, slb = i32(list(range(B))), i32(list(range(B + 1))), i32(list(range(B)))
+            us = _time_graph(lambda i: K.diag_scan(a[:B], b[:B], y[:B], None, outw[:B], st, cub, slb, sotb, B, B))
+            print(f"vector scan decode  batch {B:2d}: {us:6.1f} us", flush=True)
+        # ---- the matrix-state recurrence with step sizes
+        inner, gn = SH * SP, SG * SN
+        xc = torch.randn(T, inner + 2 * gn, device=dev) * 0.5
+        xd = (torch.randn(T, SH, device=dev) - 2.0).to(torch.bfloat16)
+        raw = torch.empty(T, inner, device=dev)
+        sst = torch.zeros(64, SH, SN, SP, device=dev)
+        dtb, na = torch.zeros(SH, device=dev), -torch.rand(SH, device=dev)
+        scratch = torch.empty(K.stepsize_scan_scratch(T, 1, SH, SN, SP, 64), device=dev)
+        us = _time_graph(lambda i: K.stepsize_scan(xc, inner, inner + gn, xd, 0, raw, sst, cu, zero, sot, dtb, na, T, 1, SH, SG, SN, SP,
+                                                   chunk=64, scratch=scratch), reps=10)
+        flops = 2 * T * SH * 2 * SN * SP
+        print(f"step-size scan prompt  heads={SH} state={SN} vdim={SP} T={T} (chunks, the rows walked twice): {us:8.1f} us  "
+              f"{flops / us / 1e6:6.2f} TFLOP/s ({flops / us / 1e6 / fp32_tflops:.2f} of the float32 rate)", flush=True)
+        us = _time_graph(lambda i: K.stepsize_scan(xc, inner, inner + gn, xd, 0, raw, sst, cu, zero, sot, dtb, na, T, 1, SH, SG, SN, SP), reps=3)
+        print(f"   row by row: {us:8.1f} us", flush=True)
+        for B in (8, 64):
+            sotb, cub, slb = i32(list(range(B))), i32(list(range(B + 1))), i32(list(range(B)))
+            us = _time_graph(lambda i: K.stepsize_scan(xc[:B], inner, inner + gn, xd[:B], 0, raw[:B], sst, cub, slb, sotb, dtb, na, B, B,
+                                                       SH, SG, SN, SP))
+            nbytes = B * 2 * SH * SN * SP * 4
+            print(f"step-size scan decode  batch {B:2d}: {us:6.1f} us  {nbytes / us / 1e3:7.1f} GB/s ({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)
+        # ---- the small kernels on T rows of width W
+        x = torch.randn(T, W, device=dev)
+        yy = torch.randn(T, W, device=dev)
+        wv = torch.ones(W, device=dev)
+        hb = torch.empty(T, W, device=dev, dtype=torch.bfloat16)
+        shift_state = torch.zeros(64, W, device=dev)
+        us = _time_graph(lambda i: K.rmsnorm_add(x, yy, wv, 1e-6, zero_y=False, groups=8), reps=10)
+        print(f"norm in 8 groups + add  {T} x {W}: {us:6.1f} us  {T * W * 4 * 3 / us / 1e3 / hbm:.2f} of the copy bandwidth", flush=True)
+        us = _time_graph(lambda i: K.token_shift(x, hb, wv, shift_state, cu, zero, sot, T, 1, max_new=T), reps=10)
+        print(f"token shift             {T} x {W}: {us:6.1f} us  {T * W * 6 / us / 1e3 / hbm:.2f}", flush=True)
+        hist = torch.zeros(9, T, W, device=dev)
+        cf = torch.full((9,), 1.0 / 9, device=dev)
+        us = _time_graph(lambda i: K.depth_mix(hist, x, cf, 8, 9), reps=10)
+        print(f"sum over depth, 9 terms {T} x {W}: {us:6.1f} us  {T * W * 4 * 10 / us / 1e3 / hbm:.2f}", flush=True)
+        cw = torch.randn(4, W, device=dev) * 0.3
+        cst = torch.zeros(64, 3, W, device=dev)
+        us = _time_graph(lambda i: K.column_conv(hb, yy, cw, wv, None, cst, cu, zero, sot, T, 1, act=1, max_new=T), reps=10)
+        print(f"convolution, 4 taps     {T} x {W}: {us:6.1f} us  {T * W * 6 / us / 1e3 / hbm:.2f}", flush=True)
+        for B in (8, 64):
+            sotb, cub, slb = i32(list(range(B))), i32(list(range(B + 1))), i32(list(range(B)))
+            t1 = _time_graph(lambda i: K.rmsnorm_add(x[:B], yy[:B], wv, 1e-6, zero_y=True, groups=8))
+            t2 = _time_graph(lambda i: K.token_shift(x[:B], hb[:B], wv, shift_state, cub, slb, sotb, B, B, max_new=1))
+            t3 = _time_graph(lambda i: K.depth_mix(hist[:, :B], x[:B], cf, 8, 9)) if False else 0.0
+            t4 = _time_graph(lambda i: K.column_conv(hb[:B], yy[:B], cw, wv, None, cst, cub, slb, sotb, B, B, act=1, max_new=1))
+            print(f"decode batch {B:2d}: norm+add {t1:5.1f} us, token shift {t2:5.1f} us, convolution {t4:5.1f} us", flush=True)
+        torch.cuda.empty_cache()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample", "latent", "retention", "recurrence"])
+    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample", "latent", "retention", "recurrence", "dinuzen"])
     ap.add_argument("--m", default="1,8,64", help="token counts (gemm), batch sizes (attn) or prompt lengths (prefill_attn)")
     ap.add_argument("--ctx", default="2048", help="attn: cached positions per sequence (comma separated)")
     ap.add_argument("--scratch", action="store_true", help="attn: splits merged by a second kernel instead of inside clusters")
@@ -428,6 +544,9 @@ def main() -> None:
         return
     if a.what == "recurrence":
         recurrence()
+        return
+    if a.what == "dinuzen":
+        dinuzen()
         return
     if a.what == "attn":
         for c in a.ctx.split(","):

@@ -184,8 +184,7 @@ class RoutedExperts:
         # rows on 16-byte boundaries: what the tensor-core forms (mma.sync for few pairs, tcgen05 for many) take
         self._mma = (rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16
                      and self.hidden % 8 == 0 and self.inter % 8 == 0)
-        # (the sorted form files every pair under its expert; pairs without one keep to the forms through the index)
-        if rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16 and not self.identity:
+        if rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16:
             from . import experts_grouped
             self._grouped = experts_grouped.try_make(self)
 

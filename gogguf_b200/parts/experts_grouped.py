@@ -20,7 +20,9 @@ def _s() -> int:
 class _Grouped:
     def __init__(self, part, gate_up: List[Linear], down: List[Linear]):
         self.part, self.gate_up, self.down = part, gate_up, down
-        self._host = torch.empty(part.E + 1, dtype=torch.int32, pin_memory=True)
+        # (with identity outputs the pairs that chose one are filed under one more index, behind the experts)
+        self.bins = part.E + (1 if getattr(part, "identity", 0) else 0)
+        self._host = torch.empty(self.bins + 1, dtype=torch.int32, pin_memory=True)
 
     def takes(self, ctx: StepContext) -> bool:
         return (not ctx.decode and ctx.n_tokens * self.part.top >= MIN_PAIRS
@@ -31,15 +33,19 @@ class _Grouped:
         T, W, F, E, top = ctx.n_tokens, p.hidden, p.inter, p.E, p.top
         P = T * top
         ws = ctx.ws
-        offsets = ws.get("moe_offsets", (E + 1,), torch.int32)
-        cursor = ws.get("moe_cursor", (E,), torch.int32)
+        nb = self.bins
+        if nb > E:
+            # a choice without an expert (index -1) is sorted behind the experts; its rows get no product and are zeroed
+            idx = torch.where(idx < 0, torch.full_like(idx, E), idx)
+        offsets = ws.get("moe_offsets", (nb + 1,), torch.int32)
+        cursor = ws.get("moe_cursor", (nb,), torch.int32)
         place = ws.get("moe_place", (P,), torch.int32)
         pair_of = ws.get("moe_pair_of", (P,), torch.int32)
         xs = ws.get("moe_rows_in", (P, W), torch.bfloat16)
         gu = ws.get("moe_gate_up", (P, 2 * F), torch.bfloat16)
         y = ws.get("moe_act_rows", (P, F), torch.bfloat16)
         out = ws.get("moe_rows_out", (P, W), torch.float32)
-        kernel("moe", "gg_moe_sort")(idx.data_ptr(), P, E, offsets.data_ptr(), place.data_ptr(), cursor.data_ptr(), _s())
+        kernel("moe", "gg_moe_sort")(idx.data_ptr(), P, nb, offsets.data_ptr(), place.data_ptr(), cursor.data_ptr(), _s())
         self._host.copy_(offsets, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
@@ -59,6 +65,8 @@ class _Grouped:
             n = off[e + 1] - off[e]
             if n:
                 self.down[e](y[off[e]:off[e + 1]], out[off[e]:off[e + 1]], m=n, ws=ws)
+        if nb > E and off[nb] > off[E]:
+            out[off[E]:off[nb]].zero_()
         kernel("moe", "gg_moe_combine")(out.data_ptr(), place.data_ptr(), residual.data_ptr(), T, W, top,
                                         ctx.seq_of_token.data_ptr(), 0, _s())
 

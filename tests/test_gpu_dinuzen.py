@@ -335,6 +335,26 @@ def test_whole_prompts_and_every_layer(tmp_path_factory, name, dtype):
         assert close(run_cut(st2, cache2, tokens, [len(tokens)]), want, dtype)
 
 
+def test_sorted_form_of_the_experts_with_identity_outputs(tmp_path_factory, monkeypatch):
+    """Long prompts of models with large experts sort the (token, choice) pairs by expert and run one tensor-core
+    product per expert; choices of an identity output are filed behind the experts and get no product.  The
+    threshold is lowered so that the test's small experts take that form."""
+    from gogguf_b200.parts import experts
+    monkeypatch.setattr(experts, "SORTED_FORM_MIN_WORK", 0.0)
+    folder = make_folder(tmp_path_factory.getbasetemp(), "WB", "bfloat16")
+    cfg, w = read_folder(folder)
+    tokens = random_tokens(cfg["vocab"], 300, seed=21)
+    want = plain_logits(cfg, w, tokens)
+    m, cache, st = load(folder, "bfloat16")
+    ff = m.blocks[0].feed_forward
+    assert ff.identity == 2 and ff._grouped is not None
+    got = run_cut(st, cache, tokens, [300])
+    assert close(got, want, "bfloat16"), rel_err(got, want)
+    monkeypatch.setattr(experts, "SORTED_FORM_MIN_WORK", 1e30)
+    again = run_cut(st, cache, tokens, [300])
+    assert close(again, want, "bfloat16", gauge=got), rel_err(again, want)
+
+
 @pytest.mark.parametrize("name,dtype", [("S", "float32"), ("S", "bfloat16"), ("ONE", "float32"), ("W", "float32"),
                                         ("W", "bfloat16")])
 def test_portions_and_decoding_equal_the_whole_prompt(tmp_path_factory, name, dtype):
