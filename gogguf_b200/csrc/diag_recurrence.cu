@@ -83,10 +83,10 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 }
 
 // grid (sequence, ceil(C / 256)): a thread owns one channel of one sequence and walks its rows.
-// a, b [T, C] float32; y [T, ldy] the second branch's projection in the compute dtype (its C columns start at y),
-// ybias [C] (may be null); out [T, C] in the compute dtype; state [slots][C] float32.
-template <typename T>
-__global__ void __launch_bounds__(256) diag_scan_kernel(const float* a, const float* b, const T* y, long long ldy,
+// a, b [T, C] float32; y [T, ldy] the second branch's projection, float32 or the compute dtype (its C columns start at
+// y), ybias [C] (may be null); out [T, C] in the compute dtype; state [slots][C] float32.
+template <typename TY, typename T>
+__global__ void __launch_bounds__(256) diag_scan_kernel(const float* a, const float* b, const TY* y, long long ldy,
                                                         const float* __restrict__ ybias, T* out, float* state,
                                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                                                         const int* __restrict__ seq_of_token, int C) {
@@ -106,19 +106,21 @@ __global__ void __launch_bounds__(256) diag_scan_kernel(const float* a, const fl
 #pragma unroll 4
     for (int t = start; t < end; ++t) {
         S = fmaf(a[(size_t)t * C + ch], S, b[(size_t)t * C + ch]);
-        out[(size_t)t * C + ch] = from_f<T>(S * gelu_tanh_f(to_f<T>(y[(size_t)t * ldy + ch]) + yb));
+        out[(size_t)t * C + ch] = from_f<T>(S * gelu_tanh_f(to_f<TY>(y[(size_t)t * ldy + ch]) + yb));
     }
     *sp = S;
 }
 
-GG_API gg_diag_scan(const float* a, const float* b, const void* y, long long ldy, int dtype, const float* ybias, void* out,
-                    float* state, const int* cu_seqlens, const int* slots, const int* seq_of_token, int ntok, int n_seqs,
-                    int C, cudaStream_t stream) {
+// y_dtype: the dtype of y; dtype: that of out.
+GG_API gg_diag_scan(const float* a, const float* b, const void* y, long long ldy, int y_dtype, int dtype, const float* ybias,
+                    void* out, float* state, const int* cu_seqlens, const int* slots, const int* seq_of_token, int ntok,
+                    int n_seqs, int C, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (C <= 0 || state == nullptr || ldy < C || (C + 255) / 256 > 65535) return GG_ERR_ARG;
     GG_DISPATCH_DTYPE(dtype, T,
-        gg_launch(diag_scan_kernel<T>, dim3(n_seqs, (C + 255) / 256), dim3(256), 0, stream, 1, a, b, (const T*)y, ldy, ybias,
-                  (T*)out, state, cu_seqlens, slots, seq_of_token, C));
+        GG_DISPATCH_DTYPE(y_dtype, TY,
+            gg_launch(diag_scan_kernel<TY, T>, dim3(n_seqs, (C + 255) / 256), dim3(256), 0, stream, 1, a, b, (const TY*)y, ldy,
+                      ybias, (T*)out, state, cu_seqlens, slots, seq_of_token, C)));
     return gg_last_error();
 }
 
@@ -191,8 +193,8 @@ __global__ void __launch_bounds__(256) diag_chunk_walk_kernel(float* sums, float
     *sp = S;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) diag_chunk_out_kernel(const float* a, const float* b, const float* sums, const T* y,
+template <typename TY, typename T>
+__global__ void __launch_bounds__(256) diag_chunk_out_kernel(const float* a, const float* b, const float* sums, const TY* y,
                                                              long long ldy, const float* __restrict__ ybias, T* out,
                                                              const int* __restrict__ cu_seqlens,
                                                              const int* __restrict__ seq_of_token, int n_seqs, int C) {
@@ -210,13 +212,13 @@ __global__ void __launch_bounds__(256) diag_chunk_out_kernel(const float* a, con
 #pragma unroll 8
     for (int t = t0; t < t1; ++t) {
         S = fmaf(a[(size_t)t * C + ch], S, b[(size_t)t * C + ch]);
-        out[(size_t)t * C + ch] = from_f<T>(S * gelu_tanh_f(to_f<T>(y[(size_t)t * ldy + ch]) + yb));
+        out[(size_t)t * C + ch] = from_f<T>(S * gelu_tanh_f(to_f<TY>(y[(size_t)t * ldy + ch]) + yb));
     }
 }
 
 // As gg_diag_scan; sums: scratch of (ntok / 64 + n_seqs) * 2 * C floats.
-GG_API gg_diag_scan_chunks(const float* a, const float* b, const void* y, long long ldy, int dtype, const float* ybias,
-                           void* out, float* sums, float* state, const int* cu_seqlens, const int* slots,
+GG_API gg_diag_scan_chunks(const float* a, const float* b, const void* y, long long ldy, int y_dtype, int dtype,
+                           const float* ybias, void* out, float* sums, float* state, const int* cu_seqlens, const int* slots,
                            const int* seq_of_token, int ntok, int n_seqs, int C, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (C <= 0 || state == nullptr || sums == nullptr || ldy < C || (C + 255) / 256 > 65535) return GG_ERR_ARG;
@@ -226,7 +228,8 @@ GG_API gg_diag_scan_chunks(const float* a, const float* b, const void* y, long l
     gg_launch(diag_chunk_walk_kernel, dim3(n_seqs, (C + 255) / 256), dim3(256), 0, stream, 1, sums, state, cu_seqlens, slots,
               seq_of_token, C);
     GG_DISPATCH_DTYPE(dtype, T,
-        gg_launch(diag_chunk_out_kernel<T>, cgrid, dim3(256), 0, stream, 1, a, b, (const float*)sums, (const T*)y, ldy, ybias,
-                  (T*)out, cu_seqlens, seq_of_token, n_seqs, C));
+        GG_DISPATCH_DTYPE(y_dtype, TY,
+            gg_launch(diag_chunk_out_kernel<TY, T>, cgrid, dim3(256), 0, stream, 1, a, b, (const float*)sums, (const TY*)y, ldy,
+                      ybias, (T*)out, cu_seqlens, seq_of_token, n_seqs, C)));
     return gg_last_error();
 }

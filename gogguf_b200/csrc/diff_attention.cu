@@ -289,7 +289,9 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     __shared__ int info[3];
     const int g = blockIdx.y;
     if (threadIdx.x == 0) {
-        int tile = blockIdx.x, b = 0, found = 0;
+        // (the step's last tiles first: a sequence's late tiles read the most keys, and the CTAs that start first
+        // should be the long ones)
+        int tile = (int)gridDim.x - 1 - (int)blockIdx.x, b = 0, found = 0;
         for (; b < n_seqs; ++b) {
             const int n = cu_seqlens[b + 1] - cu_seqlens[b];
             const int nt = (n + tpt - 1) / tpt;

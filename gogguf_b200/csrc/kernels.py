@@ -701,10 +701,10 @@ def stepsize_finish(raw: torch.Tensor, xc: torch.Tensor, xd: torch.Tensor, z_off
     _need(raw, torch.float32, "raw")
     _need(skip, torch.float32, "skip")
     _need(weight, torch.float32, "norm weight")
-    if xd.dtype != out.dtype or not out.is_contiguous() or out.shape[-1] != heads * dv or weight.numel() != heads * dv:
+    if not out.is_contiguous() or out.shape[-1] != heads * dv or weight.numel() != heads * dv:
         raise KernelError("stepsize_finish: shapes disagree")
     kernel("recurrence", "gg_stepsize_finish")(
-        _p(raw), _p(xc), xc.stride(0), _p(xd), dtype_code(xd.dtype), xd.stride(0), int(z_off), _p(skip), _p(weight), _p(out),
+        _p(raw), _p(xc), xc.stride(0), _p(xd), dtype_code(xd.dtype), dtype_code(out.dtype), xd.stride(0), int(z_off), _p(skip), _p(weight), _p(out),
         _p(seq_of_token), int(n_tokens), int(heads), int(dv), int(norm_groups), float(eps), _stream())
 
 
@@ -732,12 +732,12 @@ def diag_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, ybias: Optional
     _need(b, torch.float32, "b")
     _need(state, torch.float32, "state")
     C = a.shape[-1]
-    if y.dtype != out.dtype or y.stride(-1) != 1 or y.shape[-1] != C or not out.is_contiguous() or out.shape[-1] != C \
-            or state.shape[-1] != C:
+    if y.stride(-1) != 1 or y.shape[-1] != C or not out.is_contiguous() or out.shape[-1] != C or state.shape[-1] != C:
         raise KernelError("diag_scan: shapes disagree")
     if ybias is not None:
         _need(ybias, torch.float32, "ybias")
-    kernel("diag_recurrence", "gg_diag_scan")(_p(a), _p(b), _p(y), y.stride(0), dtype_code(y.dtype), _p(ybias), _p(out),
+    kernel("diag_recurrence", "gg_diag_scan")(_p(a), _p(b), _p(y), y.stride(0), dtype_code(y.dtype), dtype_code(out.dtype),
+                                               _p(ybias), _p(out),
                                                _p(state), _p(cu_seqlens), _p(slots), _p(seq_of_token), int(n_tokens),
                                                int(n_seqs), C, _stream())
 
@@ -760,14 +760,14 @@ def diag_scan_chunks(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, ybias: O
     _need(state, torch.float32, "state")
     _need(scratch, torch.float32, "scratch")
     C = a.shape[-1]
-    if y.dtype != out.dtype or y.stride(-1) != 1 or y.shape[-1] != C or not out.is_contiguous() or out.shape[-1] != C \
-            or state.shape[-1] != C:
+    if y.stride(-1) != 1 or y.shape[-1] != C or not out.is_contiguous() or out.shape[-1] != C or state.shape[-1] != C:
         raise KernelError("diag_scan: shapes disagree")
     if scratch.numel() < diag_scan_chunks_scratch(n_tokens, n_seqs, C):
         raise KernelError("diag_scan: the scratch is too small")
     if ybias is not None:
         _need(ybias, torch.float32, "ybias")
-    kernel("diag_recurrence", "gg_diag_scan_chunks")(_p(a), _p(b), _p(y), y.stride(0), dtype_code(y.dtype), _p(ybias),
+    kernel("diag_recurrence", "gg_diag_scan_chunks")(_p(a), _p(b), _p(y), y.stride(0), dtype_code(y.dtype),
+                                                      dtype_code(out.dtype), _p(ybias),
                                                       _p(out), _p(scratch), _p(state), _p(cu_seqlens), _p(slots),
                                                       _p(seq_of_token), int(n_tokens), int(n_seqs), C, _stream())
 

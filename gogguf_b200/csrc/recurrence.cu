@@ -872,11 +872,11 @@ GG_API gg_stepsize_scan(const float* xc, long long ldc, int b_off, int c_off, co
 }
 
 // The finish of that form, one block per token: val = (raw + skip_h * v) * silu(z), with v the head's input row
-// (xc, float32) and z the gate's columns of the projection (xd, compute dtype); the row of H dv numbers is then cut
+// (xc, float32) and z the gate's columns of the projection (xd, float32 or the compute dtype); the row of H dv numbers is then cut
 // into `norm_groups` equal runs, each divided by its own sqrt(mean(run^2) + eps), times w [H dv]; stored in the
 // compute dtype.  The gate comes before the norm.
-template <typename T>
-__global__ void __launch_bounds__(256) stepsize_finish_kernel(const float* raw, const float* xc, long long ldc, const T* xd,
+template <typename TX, typename T>
+__global__ void __launch_bounds__(256) stepsize_finish_kernel(const float* raw, const float* xc, long long ldc, const TX* xd,
                                                               long long ldd, int z_off, const float* __restrict__ skip,
                                                               const float* __restrict__ w, T* out,
                                                               const int* __restrict__ seq_of_token, int H, int dv,
@@ -893,10 +893,10 @@ __global__ void __launch_bounds__(256) stepsize_finish_kernel(const float* raw, 
     }
     const float* r = raw + (size_t)t * n;
     const float* v = xc + (size_t)t * ldc;
-    const T* z = xd + (size_t)t * ldd + z_off;
+    const TX* z = xd + (size_t)t * ldd + z_off;
     const int gs = n / norm_groups;
     auto val = [&](int c) {
-        const float zz = to_f<T>(z[c]);
+        const float zz = to_f<TX>(z[c]);
         return (r[c] + skip[c / dv] * v[c]) * (zz * rec_sigmoid(zz));
     };
     for (int g = 0; g < norm_groups; ++g) {
@@ -911,13 +911,15 @@ __global__ void __launch_bounds__(256) stepsize_finish_kernel(const float* raw, 
     }
 }
 
-GG_API gg_stepsize_finish(const float* raw, const float* xc, long long ldc, const void* xd, int dtype, long long ldd,
-                          int z_off, const float* skip, const float* w, void* out, const int* seq_of_token, int ntok, int H,
+// x_dtype: the dtype of xd; dtype: that of out.
+GG_API gg_stepsize_finish(const float* raw, const float* xc, long long ldc, const void* xd, int x_dtype, int dtype,
+                          long long ldd, int z_off, const float* skip, const float* w, void* out, const int* seq_of_token, int ntok, int H,
                           int dv, int norm_groups, float eps, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (H <= 0 || dv <= 0 || norm_groups <= 0 || (H * dv) % norm_groups || skip == nullptr || w == nullptr) return GG_ERR_ARG;
     GG_DISPATCH_DTYPE(dtype, T,
-        gg_launch(stepsize_finish_kernel<T>, dim3(ntok), dim3(256), 0, stream, 1, raw, xc, ldc, (const T*)xd, ldd, z_off, skip,
-                  w, (T*)out, seq_of_token, H, dv, norm_groups, eps));
+        GG_DISPATCH_DTYPE(x_dtype, TX,
+            gg_launch(stepsize_finish_kernel<TX, T>, dim3(ntok), dim3(256), 0, stream, 1, raw, xc, ldc, (const TX*)xd, ldd, z_off,
+                      skip, w, (T*)out, seq_of_token, H, dv, norm_groups, eps)));
     return gg_last_error();
 }

@@ -14,8 +14,9 @@
 conv(v)_t = bias + sum_j c[:, j] v_(t - taps + 1 + j) inside a sequence (the last tap meets the token itself, zeros
 before the start).  What a layer keeps per sequence is the convolution's last taps - 1 inputs and S (two
 `StateRequest`s: the part's cache request is the pair), so prompts may come in portions and decoding goes on from
-them.  The projections of h run as one product in the compute dtype; the convolution's sums, the gates, decays,
-step sizes, the state, the outputs' norm and gate are float32 in both compute paths.
+them.  The projections of h run as one product on the compute dtype's rows and matrices and leave their float32
+sums unrounded; the convolution's sums, the gates, decays, step sizes, the state, the outputs' norm and gate are
+float32 in both compute paths.
 
 Spec parameters: hidden_size, taps, names; `rglru`: width, blocks, decay_scale (8 unless given); `mamba2`:
 num_heads, value_dim, state_dim, groups, norm_groups, eps.
@@ -101,7 +102,8 @@ class RGLRUMixer:
             raise ValueError("rglru: a layer's state cannot be read by another layer")
         tail, st = _states(cache, "rglru")
         T, C = ctx.n_tokens, self.C
-        p = ctx.ws.get("rglru_proj", (T, 2 * C), self.rt.dtype)
+        # (the projection's sums leave the product in float32: what enters the recurrence is not rounded on the way)
+        p = ctx.ws.get("rglru_proj", (T, 2 * C), torch.float32)
         self.proj(h, p, ws=ctx.ws)
         u = ctx.ws.get("rglru_u", (T, C), torch.float32)
         K.column_conv(p[:, C:], u, self.conv, self.conv_bias, self.x_bias, tail.state if tail is not None else None,
@@ -179,7 +181,7 @@ class Mamba2Mixer:
             raise ValueError("mamba2: a layer's state cannot be read by another layer")
         tail, st = _states(cache, "mamba2")
         T, H, P, N, G, inner = ctx.n_tokens, self.H, self.P, self.N, self.G, self.inner
-        p = ctx.ws.get("mamba2_proj", (T, self.proj.out_features), self.rt.dtype)
+        p = ctx.ws.get("mamba2_proj", (T, self.proj.out_features), torch.float32)
         self.proj(h, p, ws=ctx.ws)
         xc = ctx.ws.get("mamba2_conv", (T, self.conv_ch), torch.float32)
         K.column_conv(p[:, inner:inner + self.conv_ch], xc, self.conv, self.conv_bias, None,
