@@ -274,7 +274,9 @@ __device__ __forceinline__ float da_quad_sum(float v) {
 #define DA_ROWS 64
 #define DA_KEYS 64
 
-template <int D, int DV>
+// WK (tiles of at most 16 rows: decode steps): the four warps all hold the tile's rows and take 16 of a page's 64 keys
+// each; at the end their maxima, sums and weighted values are put together in shared memory.
+template <int D, int DV, bool WK>
 __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* out, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens, const int* __restrict__ page_table,
@@ -353,11 +355,14 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
 
     // this thread's two rows of its warp's sixteen
     const int gq = lane >> 2, t4 = lane & 3;
-    const int rA = warp * 16 + gq, rB = rA + 8;
+    const int rbase = WK ? 0 : warp * 16;                          // the warp's first row of the tile
+    const int kbase = WK ? warp * 16 : 0;                          // the warp's first key of a page
+    constexpr int NP = WK ? 1 : 4;                                  // runs of 16 keys the warp takes of a page
+    const int rA = rbase + gq, rB = rA + 8;
     const int posA = rA < nrows ? pos0 + rA / hpg : -1, posB = rB < nrows ? pos0 + rB / hpg : -1;
     const int loA = window > 0 ? posA - window + 1 : 0, loB = window > 0 ? posB - window + 1 : 0;
-    const int wlast = min(warp * 16 + 15, nrows - 1);
-    const int wmax = warp * 16 < nrows ? pos0 + wlast / hpg : -1;   // the warp's largest position (-1: no rows)
+    const int wlast = min(rbase + 15, nrows - 1);
+    const int wmax = rbase < nrows ? pos0 + wlast / hpg : -1;       // the warp's largest position (-1: no rows)
     float O[2][DV / 8][4];
     float mrun[2][2], lrun[2][2];
 #pragma unroll
@@ -385,27 +390,27 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
             const bf16* Vt = Vs + stage * DA_KEYS * VS;
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
-                float s[8][4];
+                float s[2 * NP][4];
 #pragma unroll
-                for (int n = 0; n < 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+                for (int n = 0; n < 2 * NP; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     uint32_t a0, a1, a2, a3;
-                    da_ldsm4(a0, a1, a2, a3, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + m * D + ks * 16 + (lane >> 4) * 8);
+                    da_ldsm4(a0, a1, a2, a3, Qs + (rbase + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + m * D + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-                    for (int np = 0; np < 4; ++np) {
+                    for (int np = 0; np < NP; ++np) {
                         uint32_t b0, b1, b2, b3;
-                        da_ldsm4(b0, b1, b2, b3, Kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * KS + m * D + ks * 16 + ((lane >> 3) & 1) * 8);
+                        da_ldsm4(b0, b1, b2, b3, Kt + (kbase + np * 16 + (lane & 7) + (lane >> 4) * 8) * KS + m * D + ks * 16 + ((lane >> 3) & 1) * 8);
                         da_mma(s[2 * np], a0, a1, a2, a3, b0, b1);
                         da_mma(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
                     }
                 }
                 float mxA = -INFINITY, mxB = -INFINITY;
 #pragma unroll
-                for (int n = 0; n < 8; ++n) {
+                for (int n = 0; n < 2 * NP; ++n) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int key = key0 + n * 8 + 2 * t4 + (e & 1);
+                        const int key = key0 + kbase + n * 8 + 2 * t4 + (e & 1);
                         float v = s[n][e] * scale;
                         if (cap > 0.f) v = cap * tanhf(v * inv_cap);
                         const bool ok = e < 2 ? (key <= posA && key >= loA) : (key <= posB && key >= loB);
@@ -423,7 +428,7 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
                 mrun[m][1] = nB;
                 float sumA = 0.f, sumB = 0.f;
 #pragma unroll
-                for (int n = 0; n < 8; ++n) {
+                for (int n = 0; n < 2 * NP; ++n) {
                     s[n][0] = expf(s[n][0] - uA); s[n][1] = expf(s[n][1] - uA);
                     s[n][2] = expf(s[n][2] - uB); s[n][3] = expf(s[n][3] - uB);
                     sumA += s[n][0] + s[n][1];
@@ -434,7 +439,7 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
 #pragma unroll
                 for (int n = 0; n < DV / 8; ++n) { O[m][n][0] *= cA; O[m][n][1] *= cA; O[m][n][2] *= cB; O[m][n][3] *= cB; }
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
+                for (int kk = 0; kk < NP; ++kk) {
                     // the weights as two bfloat16 terms, p = hi + lo, so that the product with the values takes them
                     // to sixteen bits and more
                     uint32_t ah[4], al[4];
@@ -445,7 +450,7 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
 #pragma unroll
                     for (int np = 0; np < DV / 16; ++np) {
                         uint32_t b0, b1, b2, b3;
-                        da_ldsm4_t(b0, b1, b2, b3, Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8);
+                        da_ldsm4_t(b0, b1, b2, b3, Vt + (kbase + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8);
                         da_mma(O[m][2 * np], ah[0], ah[1], ah[2], ah[3], b0, b1);
                         da_mma(O[m][2 * np + 1], ah[0], ah[1], ah[2], ah[3], b2, b3);
                         da_mma(O[m][2 * np], al[0], al[1], al[2], al[3], b0, b1);
@@ -459,6 +464,77 @@ __global__ void __launch_bounds__(128) diff_attention_mma_kernel(
     // the difference of the maps, its root mean square over the head's values, the store
     const float l1A = da_quad_sum(lrun[0][0]), l1B = da_quad_sum(lrun[0][1]);
     const float l2A = da_quad_sum(lrun[1][0]), l2B = da_quad_sum(lrun[1][1]);
+    if (WK) {
+        // the four warps' shares of the keys, put together in shared memory (the pipeline's stages are free now)
+        float* mg = reinterpret_cast<float*>(da_smem);               // [warp][16 rows][map][2 + DV]
+        __syncthreads();
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = half ? rB : rA;
+            if ((half ? posB : posA) < 0) continue;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                float* pm = mg + ((size_t)(warp * 16 + r) * 2 + m) * (2 + DV);
+                if (t4 == 0) { pm[0] = mrun[m][half]; pm[1] = half ? (m ? l2B : l1B) : (m ? l2A : l1A); }
+#pragma unroll
+                for (int n = 0; n < DV / 8; ++n) {
+                    pm[2 + n * 8 + 2 * t4] = O[m][n][2 * half];
+                    pm[2 + n * 8 + 2 * t4 + 1] = O[m][n][2 * half + 1];
+                }
+            }
+        }
+        __syncthreads();
+        for (int r = warp; r < nrows; r += 4) {                     // a warp a row
+            float M[2], L[2], f[2][4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                M[m] = -INFINITY;
+                L[m] = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) M[m] = fmaxf(M[m], mg[((size_t)(w * 16 + r) * 2 + m) * (2 + DV)]);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float* pm = mg + ((size_t)(w * 16 + r) * 2 + m) * (2 + DV);
+                    f[m][w] = pm[0] == -INFINITY ? 0.f : expf(pm[0] - M[m]);
+                    L[m] += pm[1] * f[m][w];
+                }
+            }
+            const int tok = t0 + r / hpg, head = g * hpg + r % hpg;
+            float df[DV / 32];
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < DV / 32; ++k) {
+                const int c = lane + 32 * k;
+                float a[2] = {0.f, 0.f};
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) a[m] += mg[((size_t)(w * 16 + r) * 2 + m) * (2 + DV) + 2 + c] * f[m][w];
+                if (nsplit > 1) {
+                    float* base = partial + (((size_t)tok * H + head) * nsplit + blockIdx.z) * 2 * (2 + DV);
+                    base[2 + c] = a[0];
+                    base[(2 + DV) + 2 + c] = a[1];
+                } else {
+                    df[k] = a[0] / L[0] - lambda * a[1] / L[1];
+                    ss = fmaf(df[k], df[k], ss);
+                }
+            }
+            if (nsplit > 1) {
+                if (lane < 2) {
+                    float* base = partial + (((size_t)tok * H + head) * nsplit + blockIdx.z) * 2 * (2 + DV) + lane * (2 + DV);
+                    base[0] = M[lane];
+                    base[1] = L[lane];
+                }
+            } else {
+                ss = warp_sum(ss);
+                const float fn = out_scale / sqrtf(ss / (float)DV + eps);
+                bf16* o = out + ((size_t)tok * H + head) * DV;
+#pragma unroll
+                for (int k = 0; k < DV / 32; ++k) o[lane + 32 * k] = __float2bfloat16_rn(df[k] * fn);
+            }
+        }
+        return;
+    }
     if (nsplit > 1) {
         // a share of the keys: each row's running maximum, sum and weighted values per map go to scratch
         // [row of the step][head][share][map][2 + DV]; diff_attention_merge_kernel puts the shares together
@@ -546,18 +622,19 @@ __global__ void __launch_bounds__(128) diff_attention_merge_kernel(const float* 
     if (i < dv) o[i] = __float2bfloat16_rn(df * out_scale / sqrtf(ss / (float)dv + eps));
 }
 
-template <int D, int DV>
+template <int D, int DV, bool WK>
 static int da_mma_launch(const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* out, const int* positions,
                          const int* seq_of_token, const int* cu_seqlens, const int* page_table, int max_pages, int n_pages,
                          int ntok, int n_seqs, int H, int G, float scale, float cap, int window, float lambda, float eps,
                          float out_scale, int nsplit, float* partial, int* status, cudaStream_t stream) {
     const int hpg = H / G;
-    const int tpt = DA_ROWS / hpg;
-    const size_t smem = ((size_t)DA_ROWS * (2 * D + 8) + 2 * DA_KEYS * (2 * D + 8) + 2 * DA_KEYS * (DV + 8)) * sizeof(bf16);
+    const int tpt = (WK ? 16 : DA_ROWS) / hpg;
+    size_t smem = ((size_t)DA_ROWS * (2 * D + 8) + 2 * DA_KEYS * (2 * D + 8) + 2 * DA_KEYS * (DV + 8)) * sizeof(bf16);
+    if (WK) smem = max(smem, (size_t)4 * 16 * 2 * (2 + DV) * sizeof(float));      // the warps' shares, put together
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(diff_attention_mma_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(diff_attention_mma_kernel<D, DV, WK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int tiles = (ntok + tpt - 1) / tpt + n_seqs;             // an upper bound on the sequences' tiles
-    const int rc = gg_launch(diff_attention_mma_kernel<D, DV>, dim3(tiles, G, nsplit), dim3(128), smem, stream, 1, q, k_pool,
+    const int rc = gg_launch(diff_attention_mma_kernel<D, DV, WK>, dim3(tiles, G, nsplit), dim3(128), smem, stream, 1, q, k_pool,
                              v_pool, out, positions, seq_of_token, cu_seqlens, page_table, max_pages, n_seqs, H, G, hpg, tpt,
                              scale, cap, window, lambda, eps, out_scale, nsplit, partial, PageBounds{n_pages, status});
     if (rc != 0 || nsplit <= 1) return rc;
@@ -571,26 +648,30 @@ GG_API gg_diff_attention_mma_takes(int H, int G, int d, int dv, int page_size) {
     return (dims && page_size == DA_KEYS && G > 0 && H % G == 0 && H / G <= DA_ROWS && G <= 65535) ? 1 : 0;
 }
 
-// As gg_diff_attention for bfloat16 tensors, with the step's cu_seqlens [n_seqs + 1].  nsplit > 1 (steps of few
+// As gg_diff_attention for bfloat16 tensors, with the step's cu_seqlens [n_seqs + 1].  max_new: the most rows one
+// sequence brings (0: not known); where max_new * (H / G) <= 16 a tile holds 16 rows and its four warps share out every
+// page's keys.  nsplit > 1 (steps of few
 // rows and long contexts): every (tile, kv head) is the work of nsplit CTAs, each with a share of the key tiles, and a
 // second kernel merges them; partial is scratch of ntok * H * nsplit * 2 * (2 + dv) floats.
 GG_API gg_diff_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
                              const int* seq_of_token, const int* cu_seqlens, const int* page_table, int max_pages,
                              int page_size, int n_pages, int ntok, int n_seqs, int H, int G, int d, int dv, float scale,
                              float cap, int window, float lambda, float eps, float out_scale, int nsplit, float* partial,
-                             int* status, cudaStream_t stream) {
+                             int max_new, int* status, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (!gg_diff_attention_mma_takes(H, G, d, dv, page_size)) return GG_ERR_ARG;
     if (nsplit < 1 || nsplit > 64 || (nsplit > 1 && partial == nullptr)) return GG_ERR_ARG;
-#define DA_GO(D_, V_) return da_mma_launch<D_, V_>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, positions, \
-        seq_of_token, cu_seqlens, page_table, max_pages, n_pages, ntok, n_seqs, H, G, scale, cap, window, lambda, eps,      \
-        out_scale, nsplit, partial, status, stream)
+    const bool wk = max_new > 0 && max_new * (H / G) <= 16;
+#define DA_ARGS (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, positions, seq_of_token, cu_seqlens, \
+        page_table, max_pages, n_pages, ntok, n_seqs, H, G, scale, cap, window, lambda, eps, out_scale, nsplit, partial, status, stream
+#define DA_GO(D_, V_) return wk ? da_mma_launch<D_, V_, true>(DA_ARGS) : da_mma_launch<D_, V_, false>(DA_ARGS)
     if (d == 32) { if (dv == 32) DA_GO(32, 32); if (dv == 64) DA_GO(32, 64); DA_GO(32, 128); }
     if (d == 64) { if (dv == 32) DA_GO(64, 32); if (dv == 64) DA_GO(64, 64); DA_GO(64, 128); }
     if (dv == 32) DA_GO(128, 32);
     if (dv == 64) DA_GO(128, 64);
     DA_GO(128, 128);
 #undef DA_GO
+#undef DA_ARGS
 }
 
 // 1 if this library was built with checked page tables (the debug build), else 0.

@@ -428,11 +428,12 @@ def diff_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
                        positions: torch.Tensor, seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor,
                        page_table: torch.Tensor, page_size: int, n_tokens: int, n_seqs: int, heads: int, kv_heads: int,
                        d: int, dv: int, scale: float, cap: float, window: int, lam: float, eps: float,
-                       out_scale: float, nsplit: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+                       out_scale: float, nsplit: int = 1, partial: Optional[torch.Tensor] = None, max_new: int = 0) -> None:
     """`diff_attention` on the tensor cores (mma.sync) for bfloat16 tensors: the query heads of a kv head and up to
     64 / (heads / kv_heads) consecutive tokens of a sequence share a CTA and every page they read.  nsplit > 1: the
     key tiles of every such CTA are shared out over nsplit CTAs and merged by a second kernel (`partial`: float32
-    scratch of `diff_attention_partial_elems`)."""
+    scratch of `diff_attention_partial_elems`).  max_new: the most rows one sequence brings, where the caller knows
+    it; with max_new * (heads / kv_heads) <= 16 a CTA holds 16 rows and its four warps share out every page's keys."""
     if nsplit > 1:
         _need(partial, torch.float32, "partial")
         if partial.numel() < diff_attention_partial_elems(n_tokens, heads, dv, nsplit):
@@ -446,7 +447,7 @@ def diff_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
         _p(q), _p(k_pool), _p(v_pool), _p(out), _p(positions), _p(seq_of_token), _p(cu_seqlens), _p(page_table),
         page_table.shape[-1], int(page_size), k_pool.shape[0], int(n_tokens), int(n_seqs), int(heads), int(kv_heads),
         int(d), int(dv), float(scale), float(cap), int(window), float(lam), float(eps), float(out_scale), int(nsplit),
-        _p(partial), _p(status_word(q.device)), _stream())
+        _p(partial), int(max_new), _p(status_word(q.device)), _stream())
 
 
 def diff_attention_partial_elems(n_tokens: int, heads: int, dv: int, nsplit: int) -> int:

@@ -450,7 +450,8 @@ def dinuzen(sizes=((16, 4, 64, 128, 2048, 32, 64, 128, 8), (32, 8, 128, 128, 409
             ns = K.diff_attention_splits(B, B, H, G, T)
             part = torch.empty(max(K.diff_attention_partial_elems(B, H, dv, ns), 1), device=dev)
             us = _time_graph(lambda i: K.diff_attention_mma(q[:B], kpool, vpool, o[:B], posb, sotb, cub, tb, ps, B, B, H, G, d, dv,
-                                                            d ** -0.5, 30.0, 0, 0.4, 1e-6, 0.7, nsplit=ns, partial=part if ns > 1 else None))
+                                                            d ** -0.5, 30.0, 0, 0.4, 1e-6, 0.7, nsplit=ns, partial=part if ns > 1 else None,
+                                                            max_new=1))
             nbytes = B * T * G * (2 * d + dv) * 2
             print(f"diff attention decode  batch {B:2d} ctx {T} ({ns} shares): {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
                   f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)

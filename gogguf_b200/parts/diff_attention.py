@@ -141,7 +141,7 @@ class DiffAttentionMixer:
                        if nsplit > 1 else None)
             K.diff_attention_mma(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, ctx.cu_seqlens, table,
                                  cache.page_size, T, ctx.n_seqs, H, G, d, dv, self.scale, self.cap, self.window, self.lam,
-                                 self.eps, self.out_scale, nsplit=nsplit, partial=partial)
+                                 self.eps, self.out_scale, nsplit=nsplit, partial=partial, max_new=int(ctx.max_new))
         else:
             K.diff_attention(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, table, cache.page_size, T, H, G, d, dv,
                              self.scale, self.cap, self.window, self.lam, self.eps, self.out_scale)

@@ -181,7 +181,7 @@ def test_differential_attention_on_the_tensor_cores_against_the_plain_kernel(H, 
     tables = [perm[0:8], perm[8:16], perm[16:24]]
     table = _i32(tables)
     done = [0, 0, 0]
-    for lens in ((130, 1, 67), (65, 200, 2), (1, 1, 1), (1, 1, 1)):
+    for lens in ((130, 1, 67), (65, 200, 2), (1, 1, 1), (2, 1, 3), (1, 1, 1)):
         cu, sot, cul = _batch(lens)
         T = sum(lens)
         pos = _i32([done[b] + i for b, n in enumerate(lens) for i in range(n)])
@@ -196,6 +196,13 @@ def test_differential_attention_on_the_tensor_cores_against_the_plain_kernel(H, 
         K.diff_attention_mma(q, kpool, vpool, c_, pos, sot, cu, table, ps, T, 3, H, G, d, dv, 0.11, cap, window, 0.37, 1e-6, 0.8,
                              nsplit=3, partial=shares)
         assert float(((c_.float() - b_.float()).abs().max(dim=-1).values / a.float().abs().max()).max()) < 1.2e-2
+        if max(lens) * (H // G) <= 16:
+            # tiles of at most 16 rows (decode steps): the four warps share out every page's keys
+            for ns in (1, 3):
+                d_ = torch.empty_like(a)
+                K.diff_attention_mma(q, kpool, vpool, d_, pos, sot, cu, table, ps, T, 3, H, G, d, dv, 0.11, cap, window, 0.37, 1e-6,
+                                     0.8, nsplit=ns, partial=shares if ns > 1 else None, max_new=max(lens))
+                assert float(((d_.float() - b_.float()).abs().max(dim=-1).values / a.float().abs().max()).max()) < 1.2e-2, ns
         err = (a.float() - b_.float()).abs().max(dim=-1).values / a.float().abs().max()
         assert float(err.max()) < 3e-2 and float(err.median()) < 1e-2, (float(err.max()), float(err.median()), lens)   # (an output rounds to 2^-8 of itself)
         done = [x + n for x, n in zip(done, lens)]
