@@ -254,9 +254,10 @@ class DinuzenConfig:
                     raise ConfigError(f"dinuzen config: {where}.mixer.kv_from={j} must name an earlier attention layer "
                                       "with keys and values of its own")
                 a, b = mixer, src.mixer
-                if (a.kv_heads, a.dim, a.vdim, a.rot) != (b.kv_heads, b.dim, b.vdim, b.rot):
+                # (the keys come rotated as layer j rotated them; this layer's own `rot` turns its queries)
+                if (a.kv_heads, a.dim, a.vdim) != (b.kv_heads, b.dim, b.vdim):
                     raise ConfigError(f"dinuzen config: {where}.mixer reads the keys and values of layer {j}; kv_heads, "
-                                      "dim, vdim and rot must equal that layer's")
+                                      "dim and vdim must equal that layer's")
             mlp = ld.get("mlp")
             layers.append(DinuzenLayer(type=kind, mixer=mixer,
                                        mlp=None if mlp is None else FeedForwardConfig.from_dict(mlp, where + ".mlp")))

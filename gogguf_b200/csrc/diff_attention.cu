@@ -19,7 +19,7 @@
 #include "common.cuh"
 
 #define DA_WARPS 4
-#define DA_MAXDV 256
+#define DA_MAXDV 512
 
 template <typename T>
 __global__ void __launch_bounds__(256) diff_qk_prep_kernel(

@@ -36,7 +36,7 @@ from ..weights.loader import TensorDecl
 from .base import Linear, Runtime, StepContext
 from .registry import POSITIONS, lookup, register_mixer
 
-MAX_VALUE_DIM = 256
+MAX_VALUE_DIM = 512
 
 
 @register_mixer("diff_attention")

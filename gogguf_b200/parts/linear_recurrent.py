@@ -5,7 +5,7 @@
     u in `blocks` equal runs n:   r = sigmoid(A_n u_n + a_n),  i = sigmoid(I_n u_n + i_n)         A_n, I_n square
     log a = -c r softplus(lam)  (c = decay_scale),   S_t = a S_(t-1) + sqrt(1 - a^2) i u,   out = W_o (S_t * y)
 
-`mamba2` (state-space duality; state: a matrix [state, vdim] per head):
+`mamba2` (a selective state space with one decay per head and token; state: a matrix [state, vdim] per head):
     W_in h = [z: inner | x: inner | B: groups x state | C: groups x state | dt: heads],  inner = heads x vdim
     (x, B, C) <- silu(conv([x, B, C]));   dt <- softplus(dt + dt_bias)
     S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T,   y_t = S_t^T C_t + D_h x_t      head h reads group h / (heads / groups)

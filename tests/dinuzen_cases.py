@@ -75,10 +75,10 @@ CASE_ONE = model(97, 64, 1e-5, 1, [
 ])
 # sizes the tensor-core products take: wide matrices, rows on 16-byte boundaries
 CASE_W = model(523, 384, 3e-6, 2, [
-    layer("attention", attn(4, 2, 64, 64, 0.125, 20.0, 0.4, rot(32, 50000.0, (2.0, 256, 32.0, 1.0))), moe(128, 6, 2, 2, 1.5, 128)),
+    layer("attention", attn(4, 2, 64, 64, 0.125, 20.0, 0.4, rot(32, 40000.0, (3.0, 256, 16.0, 1.0))), moe(128, 6, 2, 2, 1.5, 128)),
     layer("rglru", lru(256, 4, 4), dense(512)),
     layer("mamba2", ssm(4, 64, 64, 2, 2, 4), moe(64, 8, 0, 3, 2.0, 64)),
-    layer("attention", attn(8, 2, 64, 64, 0.125, 20.0, 0.4, rot(32, 50000.0, (2.0, 256, 32.0, 1.0)), kv_from=0), dense(256)),
+    layer("attention", attn(8, 2, 64, 64, 0.125, 20.0, 0.4, rot(32, 40000.0, (3.0, 256, 16.0, 1.0)), kv_from=0), dense(256)),
 ])
 
 

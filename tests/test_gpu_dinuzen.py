@@ -268,6 +268,7 @@ ALONE = {
     "attention": _one_layer("attention", attn(6, 2, 12, 20, 0.3, 15.0, 0.3, rot(8, 10000.0, (4.0, 64, 16.0, 2.0)))),
     "attention_wide": _one_layer("attention", attn(4, 1, 64, 128, 0.125, 20.0, 0.5, rot(64, 1e6)), width=128),
     "attention_plain_scores": _one_layer("attention", attn(2, 2, 8, 8, 0.35, 0.0, 0.0, rot(0, 0.0))),
+    "attention_long_values": _one_layer("attention", attn(2, 1, 24, 320, 0.2, 12.0, 0.1, rot(12, 3000.0))),
     "rglru": _one_layer("rglru", lru(60, 3, 4)),
     "rglru_wide": _one_layer("rglru", lru(512, 2, 4), width=128),
     "rglru_one": _one_layer("rglru", lru(40, 1, 1)),
