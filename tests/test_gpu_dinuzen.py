@@ -1,7 +1,6 @@
 """The Dinuzen decoder through the framework against the plain implementation (tests/plain_dinuzen.py): each
 mechanism alone, whole prompts layer by layer, portions, decoding, unequal batches, reuse of slots, pages and states,
 far keys and page borders made to stand out, the first tokens, other sizes, the entry point, the replay program."""
-import copy
 import math
 import os
 
